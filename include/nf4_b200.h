@@ -1,0 +1,94 @@
+/*
+ * C ABI of libnf4_b200.so -- the sm_100a kernels behind Thunder's NF4 quantized-linear path.
+ *
+ * Every entry point replaces one call the reference makes into the bitsandbytes package
+ * (the reference has no FFI of its own: thunder/transforms/quantization.py is pure Python
+ * and reaches CUDA only through those calls).  All pointers are DEVICE pointers unless a
+ * parameter is named host_*; `stream` is a cudaStream_t passed as void* (NULL = the legacy
+ * default stream).  Functions return 0 on success or an NF4_ERR_* code, never throw, never
+ * synchronise the device and never allocate device memory (the caller owns every buffer), so
+ * they may be called while a stream is being captured into a CUDA graph.
+ * nf4_b200_last_error() gives the message of the last failure on the calling thread.
+ *
+ * Tensor contract (thunder/transforms/quantization.py:86-101): a weight W[N,K] (row-major,
+ * numel = N*K) is stored as
+ *     packed  uint8 [ceil(numel/2)]     byte j = (index[2j] << 4) | index[2j+1]
+ *     absmax  fp32  [ceil(numel/blocksize)]   one scale per `blocksize` consecutive elements
+ *     code16  fp32  [16]                the level table (the op's `quant_map` argument)
+ */
+#ifndef NF4_B200_H
+#define NF4_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    NF4_OK = 0,
+    NF4_ERR_ARG = 1,       /* null pointer, negative extent, unsupported dtype/blocksize */
+    NF4_ERR_ALIGN = 2,     /* a pointer breaks the documented alignment */
+    NF4_ERR_WORKSPACE = 3, /* workspace too small */
+    NF4_ERR_CUDA = 4,      /* a CUDA runtime call failed (message holds cudaGetErrorString) */
+    NF4_ERR_ARCH = 5,      /* the current device is not compute capability 10.x */
+    NF4_ERR_LIMIT = 6      /* a size exceeds a documented maximum */
+};
+
+/* element types of weights / activations / outputs */
+enum { NF4_F32 = 0, NF4_F16 = 1, NF4_BF16 = 2 };
+
+int nf4_b200_version(void);
+
+/* Copies the calling thread's last error message (NUL terminated) into buf; returns its length. */
+int nf4_b200_last_error(char* buf, int buflen);
+
+/*
+ * Blockwise NF4 quantization.  Replaces bitsandbytes.functional.quantize_4bit(w, quant_type="nf4")
+ * as called at thunder/transforms/quantization.py:63.
+ *   w       [numel] of w_dtype, contiguous
+ *   packed  [ceil(numel/2)] out, absmax [ceil(numel/blocksize)] out
+ * blocksize: power of two, 64..4096.  Results are bit-exact with the CPU oracle: fp32 absmax,
+ * IEEE division, nearest level with the lower index winning a tie, all-zero block -> level 0.0.
+ */
+int nf4_b200_quantize(const void* w, int64_t numel, int w_dtype, int blocksize, const float* code16,
+                      uint8_t* packed, float* absmax, void* stream);
+
+/*
+ * Blockwise dequantization: out[i] = round_to(out_dtype, code16[index[i]] * absmax[i / blocksize]).
+ * Replaces the dequantize step inside bitsandbytes.matmul_4bit (thunder/transforms/quantization.py:39)
+ * and bitsandbytes.functional.dequantize_4bit.
+ */
+int nf4_b200_dequantize(const uint8_t* packed, const float* absmax, const float* code16, int64_t numel,
+                        int blocksize, void* out, int out_dtype, void* stream);
+
+/*
+ * y[M,N] = x[M,K] . dequant(W[N,K])^T (+ bias[N]).  Replaces bitsandbytes.matmul_4bit(x, qweight.t(),
+ * bias=, quant_state=) as called by bnb_matmul_nf4_impl (thunder/transforms/quantization.py:34-39).
+ *   x, y, bias  of `dtype` (x row stride = K, y row stride = N); bias may be NULL
+ *   workspace   device scratch of at least nf4_b200_linear_workspace_bytes(M, N, K, dtype) bytes
+ *               (may be NULL when that is 0)
+ * Dispatch: M <= 16 with K % 64 == 0, blocksize 64 and 16-bit dtype -> fused dequant-GEMV
+ * (weights streamed once); larger M -> tensor-core dequant-GEMM; anything else (fp32, ragged K,
+ * other blocksizes) -> a generic kernel.  fp32 accumulation everywhere.
+ */
+int nf4_b200_linear(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                    const float* code16, int64_t N, int blocksize, const void* bias, void* y, int dtype,
+                    void* workspace, int64_t workspace_bytes, void* stream);
+
+int64_t nf4_b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
+
+/* The three kernels behind nf4_b200_linear, callable directly (same argument meaning). */
+int nf4_b200_gemv(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                  const float* code16, int64_t N, const void* bias, void* y, int dtype, void* stream);
+int nf4_b200_gemm(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                  const float* code16, int64_t N, const void* bias, void* y, int dtype, void* workspace,
+                  int64_t workspace_bytes, void* stream);
+int nf4_b200_linear_generic(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                            const float* code16, int64_t N, int blocksize, const void* bias, void* y,
+                            int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NF4_B200_H */

@@ -1,0 +1,70 @@
+"""ctypes binding of libnf4_b200.so (the C ABI declared in include/nf4_b200.h).
+
+The library is the only compute path: there is no CPU or PyTorch fallback.  If the shared
+object is missing or a call returns a non-zero status, a RuntimeError is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libnf4_b200.so")
+
+NF4_F32, NF4_F16, NF4_BF16 = 0, 1, 2
+
+_c_i64 = ctypes.c_int64
+_c_int = ctypes.c_int
+_c_ptr = ctypes.c_void_p
+
+# name -> (restype, argtypes); must list every symbol include/nf4_b200.h declares
+SIGNATURES = {
+    "nf4_b200_version": (_c_int, []),
+    "nf4_b200_last_error": (_c_int, [ctypes.c_char_p, _c_int]),
+    "nf4_b200_quantize": (_c_int, [_c_ptr, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
+    "nf4_b200_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr, _c_int, _c_ptr]),
+    "nf4_b200_linear": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr, _c_ptr,
+                                 _c_int, _c_ptr, _c_i64, _c_ptr]),
+    "nf4_b200_linear_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64, _c_int]),
+    "nf4_b200_gemv": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int, _c_ptr]),
+    "nf4_b200_gemm": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int,
+                               _c_ptr, _c_i64, _c_ptr]),
+    "nf4_b200_linear_generic": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr,
+                                         _c_ptr, _c_int, _c_ptr]),
+}
+
+_lib = None
+
+
+class NF4LibraryError(RuntimeError):
+    pass
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NF4LibraryError(
+                f"{LIB_PATH} is missing: build it with lightning-thunder_b200/csrc/build.sh "
+                "(there is no fallback path for the NF4 kernels)"
+            )
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    buf = ctypes.create_string_buffer(512)
+    load().nf4_b200_last_error(buf, 512)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise NF4LibraryError(f"{what} failed with status {status}: {last_error()}")

@@ -1,0 +1,226 @@
+/*
+ * CPU oracle for the NF4 weight-only quantized-linear path.  TEST INFRASTRUCTURE ONLY:
+ * it is the checker for the CUDA kernels and the timed CPU baseline; the product never
+ * calls it.
+ *
+ * What it restates.  Thunder's transform (thunder/transforms/quantization.py:53-63) hands
+ * every nn.Linear weight to bitsandbytes.functional.quantize_4bit(w, quant_type="nf4") and
+ * stores three tensors per weight (quantization.py:86-101): uint8 codes of shape
+ * [ceil(numel/2), 1], fp32 absmax of shape [ceil(numel/64)] and the fp32 16-entry code
+ * table.  The executor op bnb_matmul_nf4 (quantization.py:29-39) computes
+ * y = x . dequant(W)^T + bias.  bitsandbytes==0.48.0 (pinned in requirements/test.txt) is
+ * not part of the Thunder source tree, so the arithmetic below restates the published NF4
+ * algorithm (Dettmers et al., "QLoRA", 2023, section 3 and appendix E):
+ *
+ *   1. flatten W row-major, cut it into consecutive blocks of `blocksize` (64) elements,
+ *      the last block may be short;
+ *   2. absmax[b] = max |w| over the block, in fp32 (exact for bf16/fp16 inputs);
+ *   3. v = w / absmax[b] with one IEEE fp32 division; an all-zero block maps every element
+ *      to the index of the level 0.0;
+ *   4. index = argmin_i |v - code[i]| evaluated in fp32, the lower index wins a tie;
+ *   5. byte j = (index[2j] << 4) | index[2j+1]; an odd tail leaves the low nibble 0;
+ *   6. dequant: code[index] * absmax[b] in fp32, one round-to-nearest-even to the output type;
+ *   7. linear: y[m][n] = round_bf16( sum_k x[m][k] * Wdeq[n][k] + bias[n] ), Wdeq already
+ *      rounded to x's type (what a dequantize-then-matmul path multiplies with).
+ *
+ * PARITY UNPINNED: the reference holds no golden bytes for this path and bitsandbytes
+ * cannot be run here; steps 3-5 are decisions of this restatement.
+ *
+ * Double quantization of absmax (not in the reference, quantization.py:84 "TODO: double
+ * quant support"): offset = fp32(sum_fp64(absmax)/count); r = absmax - offset; blocks of 256;
+ * scale2 = max|r|; index8 = nearest entry of a 256-entry sorted table to r/scale2 (lower
+ * index wins a tie); dequant absmax = code256[index8] * scale2 + offset.
+ *
+ * Build: see oracle/Makefile (gcc -O3 -fopenmp -shared).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+static inline float bf16_bits_to_f32(uint16_t h) {
+    uint32_t u = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* round-to-nearest-even fp32 -> bf16 bits (finite inputs; NaN kept quiet) */
+static inline uint16_t f32_to_bf16_bits(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7fffu + lsb;
+    return (uint16_t)(u >> 16);
+}
+
+static inline int nearest_level(float v, const float* code, int n) {
+    int best = 0;
+    float bd = fabsf(v - code[0]);
+    for (int i = 1; i < n; ++i) {
+        float d = fabsf(v - code[i]);
+        if (d < bd) { bd = d; best = i; }
+    }
+    return best;
+}
+
+static inline int zero_level(const float* code, int n) {
+    for (int i = 0; i < n; ++i) if (code[i] == 0.0f) return i;
+    return nearest_level(0.0f, code, n);
+}
+
+/* steps 1-5.  w: fp32 (already widened exactly from the stored dtype). */
+void nf4_oracle_quantize_f32(const float* w, int64_t numel, int blocksize, const float* code16,
+                             uint8_t* packed, float* absmax) {
+    int64_t nblocks = (numel + blocksize - 1) / blocksize;
+    int zidx = zero_level(code16, 16);
+    int64_t nbytes = (numel + 1) / 2;
+    memset(packed, 0, (size_t)nbytes);
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nblocks; ++b) {
+        int64_t lo = b * blocksize, hi = lo + blocksize;
+        if (hi > numel) hi = numel;
+        float am = 0.0f;
+        for (int64_t i = lo; i < hi; ++i) {
+            float a = fabsf(w[i]);
+            if (a > am) am = a;
+        }
+        absmax[b] = am;
+        /* blocksize is even, so a byte never straddles two blocks */
+        for (int64_t i = lo; i < hi; ++i) {
+            int idx = (am == 0.0f) ? zidx : nearest_level(w[i] / am, code16, 16);
+            if (i & 1) packed[i >> 1] |= (uint8_t)idx;
+            else packed[i >> 1] |= (uint8_t)(idx << 4);
+        }
+    }
+}
+
+void nf4_oracle_quantize_bf16(const uint16_t* w, int64_t numel, int blocksize, const float* code16,
+                              uint8_t* packed, float* absmax) {
+    int64_t nblocks = (numel + blocksize - 1) / blocksize;
+    int zidx = zero_level(code16, 16);
+    memset(packed, 0, (size_t)((numel + 1) / 2));
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nblocks; ++b) {
+        int64_t lo = b * blocksize, hi = lo + blocksize;
+        if (hi > numel) hi = numel;
+        float am = 0.0f;
+        for (int64_t i = lo; i < hi; ++i) {
+            float a = fabsf(bf16_bits_to_f32(w[i]));
+            if (a > am) am = a;
+        }
+        absmax[b] = am;
+        for (int64_t i = lo; i < hi; ++i) {
+            int idx = (am == 0.0f) ? zidx : nearest_level(bf16_bits_to_f32(w[i]) / am, code16, 16);
+            if (i & 1) packed[i >> 1] |= (uint8_t)idx;
+            else packed[i >> 1] |= (uint8_t)(idx << 4);
+        }
+    }
+}
+
+/* step 6, fp32 result before the final rounding */
+void nf4_oracle_dequantize_f32(const uint8_t* packed, const float* absmax, const float* code16,
+                               int64_t numel, int blocksize, float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < numel; ++i) {
+        uint8_t byte = packed[i >> 1];
+        int idx = (i & 1) ? (byte & 15) : (byte >> 4);
+        out[i] = code16[idx] * absmax[i / blocksize];
+    }
+}
+
+void nf4_oracle_dequantize_bf16(const uint8_t* packed, const float* absmax, const float* code16,
+                                int64_t numel, int blocksize, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < numel; ++i) {
+        uint8_t byte = packed[i >> 1];
+        int idx = (i & 1) ? (byte & 15) : (byte >> 4);
+        out[i] = f32_to_bf16_bits(code16[idx] * absmax[i / blocksize]);
+    }
+}
+
+/* step 7 for bf16 activations: x [M,K], packed W [N,K] row-major flattened, y [M,N] bf16 bits.
+ * The dequantised row is rounded to bf16 first; accumulation is fp32 in 8 lanes. */
+void nf4_oracle_linear_bf16(const uint16_t* x, int64_t M, int64_t K, const uint8_t* packed,
+                            const float* absmax, const float* code16, int64_t N, int blocksize,
+                            const uint16_t* bias, uint16_t* y) {
+#pragma omp parallel
+    {
+        float wrow[K];
+#pragma omp for schedule(static)
+        for (int64_t n = 0; n < N; ++n) {
+            for (int64_t k = 0; k < K; ++k) {
+                int64_t i = n * K + k;
+                uint8_t byte = packed[i >> 1];
+                int idx = (i & 1) ? (byte & 15) : (byte >> 4);
+                wrow[k] = bf16_bits_to_f32(f32_to_bf16_bits(code16[idx] * absmax[i / blocksize]));
+            }
+            for (int64_t m = 0; m < M; ++m) {
+                const uint16_t* xr = x + m * K;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                int64_t k = 0;
+                for (; k + 8 <= K; k += 8)
+                    for (int j = 0; j < 8; ++j) acc[j] += bf16_bits_to_f32(xr[k + j]) * wrow[k + j];
+                float s = ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
+                for (; k < K; ++k) s += bf16_bits_to_f32(xr[k]) * wrow[k];
+                if (bias) s += bf16_bits_to_f32(bias[n]);
+                y[m * N + n] = f32_to_bf16_bits(s);
+            }
+        }
+    }
+}
+
+/* fp32 activations / fp32 dequantised weights (the reference's fp32 MLP test case,
+ * thunder/tests/test_transforms.py:189-230). */
+void nf4_oracle_linear_f32(const float* x, int64_t M, int64_t K, const uint8_t* packed,
+                           const float* absmax, const float* code16, int64_t N, int blocksize,
+                           const float* bias, float* y) {
+#pragma omp parallel for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+        for (int64_t m = 0; m < M; ++m) {
+            double s = 0.0;
+            for (int64_t k = 0; k < K; ++k) {
+                int64_t i = n * K + k;
+                uint8_t byte = packed[i >> 1];
+                int idx = (i & 1) ? (byte & 15) : (byte >> 4);
+                s += (double)x[m * K + k] * (double)(code16[idx] * absmax[i / blocksize]);
+            }
+            if (bias) s += bias[n];
+            y[m * N + n] = (float)s;
+        }
+    }
+}
+
+/* ---- double quantization of absmax ------------------------------------------------------ */
+
+void nf4_oracle_dq_quantize(const float* absmax, int64_t nblocks, int blocksize2, const float* code256,
+                            uint8_t* absmax_u8, float* scale2, float* offset_out) {
+    double sum = 0.0;
+    for (int64_t i = 0; i < nblocks; ++i) sum += (double)absmax[i];
+    float offset = nblocks ? (float)(sum / (double)nblocks) : 0.0f;
+    *offset_out = offset;
+    int64_t nb2 = (nblocks + blocksize2 - 1) / blocksize2;
+    int zidx = zero_level(code256, 256);
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < nb2; ++b) {
+        int64_t lo = b * blocksize2, hi = lo + blocksize2;
+        if (hi > nblocks) hi = nblocks;
+        float am = 0.0f;
+        for (int64_t i = lo; i < hi; ++i) {
+            float a = fabsf(absmax[i] - offset);
+            if (a > am) am = a;
+        }
+        scale2[b] = am;
+        for (int64_t i = lo; i < hi; ++i)
+            absmax_u8[i] = (uint8_t)((am == 0.0f) ? zidx : nearest_level((absmax[i] - offset) / am, code256, 256));
+    }
+}
+
+void nf4_oracle_dq_dequantize(const uint8_t* absmax_u8, const float* scale2, float offset, const float* code256,
+                              int64_t nblocks, int blocksize2, float* absmax) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < nblocks; ++i)
+        absmax[i] = fmaf(code256[absmax_u8[i]], scale2[i / blocksize2], offset);
+}
+
+int nf4_oracle_version(void) { return 1; }

@@ -1,0 +1,146 @@
+"""GPU parity of the NF4 linear (GEMV / GEMM / generic kernels) against the CPU oracle, through
+the C ABI.  Tolerance on outputs: rtol 1.6e-2, atol 1e-2 (bf16), as the task's north star states."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import bf16_bits, bits_to_bf16, seeded_act, seeded_weight, sha256
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+RTOL, ATOL = 1.6e-2, 1e-2
+
+
+def _oracle_linear(x_cpu, packed_np, absmax_np, code, N, K, bias_cpu=None):
+    if x_cpu.dtype == torch.bfloat16:
+        y = oracle.linear_bf16(bf16_bits(x_cpu), packed_np, absmax_np, code, N, K, 64,
+                               None if bias_cpu is None else bf16_bits(bias_cpu))
+        return bits_to_bf16(y).float()
+    y = oracle.linear_f32(x_cpu.float().numpy(), packed_np, absmax_np, code, N, K, 64,
+                          None if bias_cpu is None else bias_cpu.float().numpy())
+    return torch.from_numpy(y)
+
+
+def _check(x_cpu, w_cpu, code, bias_cpu=None, blocksize=64):
+    import nf4_b200
+
+    N, K = w_cpu.shape
+    packed, qs = nf4_b200.quantize_4bit(w_cpu.cuda(), blocksize=blocksize)
+    bias = None if bias_cpu is None else bias_cpu.cuda()
+    y = nf4_b200.matmul_4bit(x_cpu.cuda(), packed.t(), bias=bias, quant_state=qs)
+    torch.cuda.synchronize()
+    assert y.shape == (*x_cpu.shape[:-1], N) and y.dtype == x_cpu.dtype
+    p_np, a_np = packed.cpu().numpy(), qs.absmax.cpu().numpy()
+    if blocksize == 64:
+        ref = _oracle_linear(x_cpu.reshape(-1, K), p_np, a_np, code, N, K, bias_cpu)
+    else:
+        wd = oracle.dequantize(p_np, a_np, code, N * K, blocksize, out="f32").reshape(N, K)
+        ref = torch.from_numpy(x_cpu.float().numpy().reshape(-1, K).astype(np.float64) @ wd.astype(np.float64).T).float()
+        if bias_cpu is not None:
+            ref += bias_cpu.float()
+    got = y.float().cpu().reshape(-1, N)
+    torch.testing.assert_close(got, ref, rtol=RTOL, atol=ATOL)
+    return y
+
+
+def test_config1_linear_golden(nf4_code_np):
+    """BASELINE config 1: y = x . W_deq^T with x [16,4096]; also pinned against the golden y."""
+    with open(os.path.join(GOLDEN, "config1.json")) as f:
+        g = json.load(f)
+    N, K = g["shape"]
+    w = seeded_weight((N, K), g["seed_w"])
+    x = seeded_act((16, K), g["seed_x"])
+    y = _check(x, w, nf4_code_np)
+    gold = np.frombuffer(bytes.fromhex(g["y_bf16_row0_head_hex"]), dtype=np.uint16)
+    torch.testing.assert_close(y[0, :32].float().cpu(), bits_to_bf16(gold).float(), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8, 9, 15, 16])
+@pytest.mark.parametrize("N,K", [(256, 256), (1000, 512), (4096, 4096), (300, 14336), (16, 64), (1, 128), (37, 7168)])
+def test_gemv_shapes(nf4_code_np, M, N, K):
+    w = seeded_weight((N, K), N * 7 + K)
+    x = seeded_act((M, K), M)
+    _check(x, w, nf4_code_np)
+
+
+@pytest.mark.parametrize("plan", ["1,0", "1,2", "2,1", "2,4", "4,0", "4,3"])
+def test_gemv_every_plan(nf4_code_np, plan, monkeypatch):
+    """Forces each (rows-per-warp, K-split) variant of the GEMV on the same problem."""
+    monkeypatch.setenv("NF4_GEMV_PLAN", plan)
+    w = seeded_weight((1500, 2048), 17)
+    for M in (1, 5, 12):
+        _check(seeded_act((M, 2048), M + 100), w, nf4_code_np)
+
+
+def test_gemv_bias_fp16_and_batch_dims(nf4_code_np):
+    w = seeded_weight((512, 1024), 3, dtype=torch.float16)
+    x = seeded_act((2, 3, 1024), 4, dtype=torch.float16)
+    b = seeded_act((512,), 5, dtype=torch.float16)
+    _check(x, w, nf4_code_np, bias_cpu=b)
+    wb = seeded_weight((512, 1024), 3)
+    _check(seeded_act((1, 1, 1024), 6), wb, nf4_code_np, bias_cpu=seeded_act((512,), 7))
+
+
+def test_gemv_is_deterministic(nf4_code_np):
+    import nf4_b200
+
+    w = seeded_weight((4096, 4096), 21).cuda()
+    x = seeded_act((1, 4096), 22).cuda()
+    packed, qs = nf4_b200.quantize_4bit(w)
+    y0 = nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs)
+    for _ in range(5):
+        assert torch.equal(nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs), y0)
+
+
+@pytest.mark.parametrize("M", [17, 64, 256])
+@pytest.mark.parametrize("N,K", [(512, 1024), (4096, 4096)])
+def test_gemm_shapes(nf4_code_np, M, N, K):
+    w = seeded_weight((N, K), N + K)
+    x = seeded_act((M, K), M)
+    _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(3, 2, 2), (1, 512, 512), (5, 33, 100), (20, 70, 130)])
+def test_generic_kernel_ragged_shapes(nf4_code_np, dtype, M, N, K):
+    """fp32 and K % 64 != 0 (the reference tests use Linear(2,2) and an fp32 512->1024 MLP)."""
+    w = seeded_weight((N, K), N * K, std=0.3, dtype=dtype)
+    x = seeded_act((M, K), M + K, dtype=dtype)
+    b = seeded_act((N,), 1, dtype=dtype)
+    _check(x, w, nf4_code_np, bias_cpu=b)
+
+
+def test_other_blocksize_uses_generic(nf4_code_np):
+    w = seeded_weight((128, 512), 8)
+    _check(seeded_act((4, 512), 2), w, nf4_code_np, blocksize=128)
+
+
+def test_linearity_at_full_size(nf4_code_np):
+    """Size-independent property on the metric's GEMV shape (14336x4096, M=1):
+    f(a*x1 + x2) ~= a*f(x1) + f(x2), and a permutation check against the dequantised matrix."""
+    import nf4_b200
+
+    N, K = 14336, 4096
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w = (torch.randn((N, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    packed, qs = nf4_b200.quantize_4bit(w)
+    x1 = torch.randn((1, K), generator=g, device="cuda").to(torch.bfloat16)
+    x2 = torch.randn((1, K), generator=g, device="cuda").to(torch.bfloat16)
+    f = lambda x: nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs).float()
+    x3 = (2.0 * x1.float() + x2.float()).to(torch.bfloat16)
+    torch.testing.assert_close(f(x3), 2.0 * f(x1) + f(x2), rtol=3e-2, atol=6e-2)
+    # against an fp32 matmul on the dequantised weight (torch is only the checker here)
+    wd = nf4_b200.dequantize_4bit(packed, qs).float()
+    torch.testing.assert_close(f(x1), x1.float() @ wd.t(), rtol=RTOL, atol=ATOL)
+    # a one-hot activation reads back one dequantised column exactly (bf16 x bf16 products are exact)
+    e = torch.zeros((1, K), device="cuda", dtype=torch.bfloat16)
+    e[0, 1234] = 1.0
+    col = nf4_b200.matmul_4bit(e, packed.t(), quant_state=qs)[0]
+    ref_col = (qs.code[(packed.view(N, K // 2)[:, 617].int() >> 4).long()].to(torch.bfloat16).float()
+               * qs.absmax.view(N, K // 64)[:, 1234 // 64])
+    torch.testing.assert_close(col.float(), ref_col, rtol=8e-3, atol=1e-6)
