@@ -88,6 +88,15 @@ int nf4_b200_linear_generic(const void* x, int64_t M, int64_t K, const uint8_t* 
                             const float* code16, int64_t N, int blocksize, const void* bias, void* y,
                             int dtype, void* stream);
 
+/*
+ * Status word of the kernels that wait on in-kernel barriers (the staged GEMV).  Copies 4 words to
+ * host memory: [0] first error code (0 = none; 1/2/3 = a bounded wait on a full/empty/activation
+ * barrier ran out, 4 = unexpected shared-memory window), [1] block index, [2] pipeline stage,
+ * [3] number of waits that ran out.  SYNCHRONISES the device; for tests and diagnosis only.  No
+ * counterpart in the reference.
+ */
+int nf4_b200_device_error(unsigned int* host_out4);
+
 #ifdef __cplusplus
 }
 #endif

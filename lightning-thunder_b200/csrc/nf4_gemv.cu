@@ -24,14 +24,12 @@
 #include <cstdio>
 #include <cstdlib>
 
-#include "nf4_common.cuh"
+#include "nf4_gemv_common.cuh"
 
 namespace nf4 {
 
 constexpr int GEMV_THREADS = 512;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int GEMV_SMEM = 232448;          // 227 KB: the opt-in maximum per CTA
-constexpr int LUT_WINDOW = 65536;          // 256 entries x 256 B
 constexpr int GEMV_NSTAGE = 3;             // register stages of weight loads (NSTAGE-1 in flight)
 constexpr int X_SMEM_LIMIT = 60000;        // x is staged in shared memory when it fits below the table
 
@@ -48,43 +46,6 @@ struct GemvParams {
     int KBW;       // 64-blocks per warp = KB >> log2P
     int x_stride_bytes;  // row stride of the staged x in shared memory
 };
-
-template <typename T> struct Mma;
-template <> struct Mma<__nv_bfloat16> {
-    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
-                                               const float (&c)[4]) {
-        asm(
-            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
-    }
-    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&h);
-    }
-};
-template <> struct Mma<__half> {
-    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
-                                               const float (&c)[4]) {
-        asm(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
-    }
-    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
-        __half2 h = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&h);
-    }
-};
-
-// one table lookup: byte `SEL` of w -> two 16-bit values
-template <int SEL>
-__device__ __forceinline__ uint32_t lut_lookup(uint32_t w, uint32_t window_lane) {
-    const uint32_t addr = __byte_perm(w, window_lane, 0x7604 | (SEL << 4));
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
 
 template <int TB>
 struct GemvStage {
@@ -303,7 +264,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
 
 // ---------------------------------------------------------------------------------------------
 // Generic kernel: any K, any blocksize, fp32/fp16/bf16.  One warp per weight row, up to 16
-// activation rows per pass.  Slow path for shapes the tensor-core kernels do not take.
+// activation rows per pass.  Slow path for shapes the tensor-core kernels do not take.  Same
+// numerics as the fused GEMV: levels rounded to the activation type, fp32 scaling and sums.
 template <typename T>
 __global__ void __launch_bounds__(256) linear_generic_kernel(const T* __restrict__ x, int M, int K,
                                                              const uint8_t* __restrict__ packed,
@@ -311,7 +273,7 @@ __global__ void __launch_bounds__(256) linear_generic_kernel(const T* __restrict
                                                              const float* __restrict__ code16, int N, int blocksize,
                                                              const T* __restrict__ bias, T* __restrict__ y) {
     __shared__ float s_code[16];
-    if (threadIdx.x < 16) s_code[threadIdx.x] = code16[threadIdx.x];
+    if (threadIdx.x < 16) s_code[threadIdx.x] = Elem<T>::to_f32(Elem<T>::from_f32(code16[threadIdx.x]));
     __syncthreads();
     const int lane = threadIdx.x & 31;
     const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -419,6 +381,15 @@ static int dispatch_gemv(const GemvParams& p, const GemvPlan& pl, cudaStream_t s
 template <typename T>
 static int gemv_typed(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16,
                       int N, const void* bias, void* y, cudaStream_t stream) {
+    const char* force = getenv("NF4_GEMV_KERNEL");   // "direct" or "staged": pins the variant (tests, tuning)
+    if (!(force && force[0] == 'd')) {
+        const int rc = gemv_staged_try<T>(x, M, K, packed, absmax, code16, N, bias, y, stream);
+        if (rc >= 0) return rc;
+        if (force && force[0] == 's') {
+            set_error("gemv: the staged kernel does not take M=%d N=%d K=%d", M, N, K);
+            return NF4_ERR_ARG;
+        }
+    }
     const int NT = M <= 8 ? 1 : 2;
     GemvPlan pl = plan_gemv(M, N, K, NT);
     GemvParams p;

@@ -1,0 +1,87 @@
+// Pieces shared by the two fused dequant-GEMV kernels: the mma.sync wrapper and the
+// conflict-free byte -> (16-bit, 16-bit) lookup table in shared memory.
+#pragma once
+
+#include "nf4_common.cuh"
+
+namespace nf4 {
+
+constexpr int GEMV_SMEM = 232448;          // 227 KB: the opt-in maximum per CTA
+constexpr int LUT_WINDOW = 65536;          // 256 entries x 256 B, 64 KB aligned in the shared window
+
+template <typename T> struct Mma;
+template <> struct Mma<__nv_bfloat16> {
+    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                               const float (&c)[4]) {
+        asm(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+    }
+    // D = A*B with a zero accumulator (one register holds the zero)
+    static __device__ __forceinline__ void run0(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+    }
+    // D += A*B in place
+    static __device__ __forceinline__ void acc(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+template <> struct Mma<__half> {
+    static __device__ __forceinline__ void run(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                               const float (&c)[4]) {
+        asm(
+            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+    }
+    static __device__ __forceinline__ void run0(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+    }
+    static __device__ __forceinline__ void acc(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+};
+
+// one table lookup: byte `SEL` of w -> two 16-bit values
+template <int SEL>
+__device__ __forceinline__ uint32_t lut_lookup(uint32_t w, uint32_t window_lane) {
+    const uint32_t addr = __byte_perm(w, window_lane, 0x7604 | (SEL << 4));
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+
+// Fills the table: entry e (a packed byte) -> levels of its high and low nibble, one copy per lane.
+// Called by `nwarps` warps (warp index `warp`); lut_ptr is the generic address of the window.
+template <typename T>
+__device__ __forceinline__ void lut_build(uint8_t* lut_ptr, const float* __restrict__ code16, int warp, int nwarps, int lane) {
+    for (int e = warp; e < 256; e += nwarps) {
+        const uint32_t v = Mma<T>::pack(__ldg(code16 + (e >> 4)), __ldg(code16 + (e & 15)));
+        *reinterpret_cast<uint32_t*>(lut_ptr + e * 256 + lane * 4) = v;
+    }
+}
+
+// Staged (bulk-copy) GEMV: launches and returns NF4_OK, or returns -1 if the shape does not fit.
+template <typename T>
+int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16, int N,
+                    const void* bias, void* y, cudaStream_t stream);
+
+}  // namespace nf4

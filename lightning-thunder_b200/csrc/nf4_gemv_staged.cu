@@ -1,0 +1,565 @@
+// Fused NF4 dequant-GEMV, staged variant: packed weights and absmax travel HBM -> shared memory
+// by TMA (cp.async.bulk.tensor.2d, completion on an mbarrier, no multicast): one request moves a
+// box of 16 (or 8) weight rows x one K segment, so DRAM sees long sequential bursts, nothing
+// passes through the L1 tag stage and the data in flight lives in a shared-memory ring instead of
+// registers.  The box is 32 bytes wider than the segment (and the absmax box 4 floats wider): that
+// makes the row pitch in shared memory 32 mod 128 bytes, which keeps the fragment loads free of
+// bank conflicts without a swizzle mode.
+//
+// One CTA per SM: 16 compute warps + 1 producer warp.  A stage of the ring holds one tile of 16
+// weight rows x SB 64-blocks (SB <= 32: up to 1 KB of codes per row) plus the SB absmax values
+// of each row.  Compute warp w owns blocks w and w+16 of every stage (K is split over the warps),
+// builds the A fragments of mma.sync.m16n8k16 from the packed bytes with the conflict-free lookup
+// table (see nf4_gemv_common.cuh), multiplies them with the activation fragments (B operand, up to
+// 8 activation rows per column tile) and folds the 4 accumulators of a 64-block into the running
+// sum with that block's fp32 absmax.  Rows are processed in groups of TG tiles so an activation
+// fragment is fetched once per (group, K segment); at the end of a group the 16 partial sums per
+// output meet in shared memory, in fixed order, and leave as bf16/fp16.
+//
+// Every wait on an mbarrier is bounded (wall-clock limit); on a time-out the CTA records an error
+// code in a device word (read it with nf4_b200_device_error), stops waiting and runs to its end.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "nf4_gemv_common.cuh"
+
+namespace nf4 {
+
+constexpr int SG_MAX_STAGES = 8;
+constexpr unsigned long long SG_WAIT_LIMIT_NS = 200ull * 1000 * 1000;   // 0.2 s per wait
+
+__device__ unsigned int g_gemv_error[4];   // [0] first error code, [1] block, [2] stage, [3] count
+
+struct alignas(64) StagedParams {
+    CUtensorMap wmap16, wmap8;   // packed codes viewed as uint64 [N][K/16], boxes of 16 and 8 rows
+    CUtensorMap amap16, amap8;   // absmax fp32 [N][K/64], boxes of 16 and 8 rows
+    const void* x;
+    const uint8_t* packed;
+    const float* absmax;
+    const float* code16;
+    const void* bias;
+    void* y;
+    int M, N, K, KB;
+    int SB;          // 64-blocks per stage (divides KB, multiple of 4, <= 32)
+    int nseg;        // KB / SB
+    int NS;          // ring stages
+    int RS;          // bytes between weight rows inside a stage (SB*32 + 32)
+    int AS;          // bytes between absmax rows inside a stage (SB*4 + 16)
+    int stage_bytes; // 16*RS + 16*AS
+    int x_staged;    // activations are copied to shared memory
+    int x_stride;    // bytes between staged activation rows (2K + 16)
+    // offsets from the start of dynamic shared memory
+    int off_bars, off_part, off_x;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// Bounded wait.  Returns immediately once the CTA has given up (abort flag set).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int stage) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (*abort_flag) return;
+    const unsigned long long t0 = global_ns();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return;
+        if (global_ns() - t0 > SG_WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            if (atomicCAS(&g_gemv_error[0], 0u, (unsigned)code) == 0u) {
+                g_gemv_error[1] = blockIdx.x;
+                g_gemv_error[2] = (unsigned)stage;
+            }
+            atomicAdd(&g_gemv_error[3], 1u);
+            return;
+        }
+    }
+}
+
+// One 64-block of one 16-row tile: 16 table lookups, 4 chained MMAs per column tile, one scaling.
+// HALF: rows 8..15 of the tile do not exist (their fragment registers are zero).
+template <typename T, int NT, bool HALF>
+__device__ __forceinline__ void block_one(const uint8_t* pa, float ama, float amb, int RS, uint32_t window_lane,
+                                          const uint32_t (&xf)[NT][8], float (&acc)[NT][4]) {
+    const uint2 wa = *reinterpret_cast<const uint2*>(pa);
+    uint2 wb = make_uint2(0u, 0u);
+    if (!HALF) wb = *reinterpret_cast<const uint2*>(pa + 8 * RS);
+    float tmp[NT][4];
+    uint32_t a[4];
+    a[1] = 0u;
+    a[3] = 0u;
+    // k-step 0: bytes 0,1
+    a[0] = lut_lookup<0>(wa.x, window_lane);
+    a[2] = lut_lookup<1>(wa.x, window_lane);
+    if (!HALF) { a[1] = lut_lookup<0>(wb.x, window_lane); a[3] = lut_lookup<1>(wb.x, window_lane); }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) Mma<T>::run0(tmp[nt], a, xf[nt][0], xf[nt][1]);
+    // k-step 1: bytes 2,3
+    a[0] = lut_lookup<2>(wa.x, window_lane);
+    a[2] = lut_lookup<3>(wa.x, window_lane);
+    if (!HALF) { a[1] = lut_lookup<2>(wb.x, window_lane); a[3] = lut_lookup<3>(wb.x, window_lane); }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) Mma<T>::acc(tmp[nt], a, xf[nt][2], xf[nt][3]);
+    // k-step 2: bytes 4,5
+    a[0] = lut_lookup<0>(wa.y, window_lane);
+    a[2] = lut_lookup<1>(wa.y, window_lane);
+    if (!HALF) { a[1] = lut_lookup<0>(wb.y, window_lane); a[3] = lut_lookup<1>(wb.y, window_lane); }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) Mma<T>::acc(tmp[nt], a, xf[nt][4], xf[nt][5]);
+    // k-step 3: bytes 6,7
+    a[0] = lut_lookup<2>(wa.y, window_lane);
+    a[2] = lut_lookup<3>(wa.y, window_lane);
+    if (!HALF) { a[1] = lut_lookup<2>(wb.y, window_lane); a[3] = lut_lookup<3>(wb.y, window_lane); }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) Mma<T>::acc(tmp[nt], a, xf[nt][6], xf[nt][7]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        acc[nt][0] = fmaf(tmp[nt][0], ama, acc[nt][0]);
+        acc[nt][1] = fmaf(tmp[nt][1], ama, acc[nt][1]);
+        if (!HALF) {
+            acc[nt][2] = fmaf(tmp[nt][2], amb, acc[nt][2]);
+            acc[nt][3] = fmaf(tmp[nt][3], amb, acc[nt][3]);
+        }
+    }
+}
+
+// The BPW blocks a warp owns in a stage (off_a / off_am: this thread's byte offsets of the packed
+// bytes and the absmax value of each block inside the stage).
+template <typename T, int NT, int BPW, bool HALF>
+__device__ __forceinline__ void block_set(const uint8_t* sb, const int (&off_a)[BPW], const float (&am)[BPW][2], int RS,
+                                          uint32_t window_lane, const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4]) {
+#pragma unroll
+    for (int bi = 0; bi < BPW; ++bi)
+        block_one<T, NT, HALF>(sb + off_a[bi], am[bi][0], am[bi][1], RS, window_lane, xf[bi], acc);
+}
+
+template <typename T, int NT, int TG, int CW>
+__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __grid_constant__ StagedParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr int SG_COMPUTE_WARPS = CW;
+    constexpr int BPW = 32 / CW;          // 64-blocks of a stage per warp
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int g = lane >> 2;
+    const int q = lane & 3;
+
+    const uint32_t s0 = smem_u32(smem);
+    const uint32_t lut_base = (s0 + LUT_WINDOW - 1) & ~(uint32_t)(LUT_WINDOW - 1);
+    uint8_t* const lut_ptr = smem + (lut_base - s0);
+    uint8_t* const ring = lut_ptr + LUT_WINDOW;
+    const uint32_t ring_u32 = lut_base + LUT_WINDOW;
+    uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + p.off_bars);   // full[NS], empty[NS], xbar
+    volatile int* const abort_flag = reinterpret_cast<volatile int*>(smem + p.off_bars + (2 * SG_MAX_STAGES + 1) * 8);
+    float* const part = reinterpret_cast<float*>(smem + p.off_part);
+    const uint8_t* const xs = smem + p.off_x;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + SG_MAX_STAGES * 8, xbar = full0 + 2 * SG_MAX_STAGES * 8;
+
+    // rows are dealt out in halves of 8: a CTA owns [8*h0, 8*h1), its last tile may be a half tile
+    const int H = (p.N + 7) >> 3;
+    const int h0 = (int)(((int64_t)H * blockIdx.x) / gridDim.x);
+    const int h1 = (int)(((int64_t)H * (blockIdx.x + 1)) / gridDim.x);
+    const int r0 = h0 * 8;
+    const int r1 = min(h1 * 8, p.N);
+    const int nhalves = h1 - h0;
+    const int ntiles = (nhalves + 1) >> 1;
+    const bool last_is_half = (nhalves & 1) != 0;
+    const int ngroups = (ntiles + TG - 1) / TG;
+
+    if (s0 > 2048u) {   // the host-side map assumes the dynamic region starts within 2 KB of the window
+        if (tid == 0 && atomicCAS(&g_gemv_error[0], 0u, 4u) == 0u) g_gemv_error[1] = blockIdx.x;
+        return;
+    }
+    if (tid == 0) {
+        for (int s = 0; s < p.NS; ++s) {
+            mbar_init(full0 + s * 8, 1);
+            mbar_init(empty0 + s * 8, SG_COMPUTE_WARPS);
+        }
+        mbar_init(xbar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == SG_COMPUTE_WARPS) {
+        // ------------------------------- producer warp --------------------------------------
+        if (p.x_staged) {
+            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)(p.M * p.K * 2));
+            __syncwarp();
+            if (lane < p.M)
+                bulk_g2s(smem_u32(xs) + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * p.K * 2,
+                         (uint32_t)(p.K * 2), xbar);
+        }
+        int stage = 0, slot = 0;
+        uint32_t parity = 0;
+        for (int grp = 0; grp < ngroups; ++grp) {
+            const int nt_here = min(TG, ntiles - grp * TG);
+            for (int seg = 0; seg < p.nseg; ++seg) {
+                for (int j = 0; j < nt_here; ++j) {
+                    mbar_wait(empty0 + slot * 8, parity ^ 1u, abort_flag, 2, stage);
+                    const int tile = grp * TG + j;
+                    const int row0 = r0 + tile * 16;
+                    const bool half = last_is_half && tile == ntiles - 1;
+                    if (lane == 0) {
+                        const uint32_t fullb = full0 + slot * 8;
+                        const uint32_t sbase = ring_u32 + (uint32_t)slot * (uint32_t)p.stage_bytes;
+                        mbar_expect_tx(fullb, (uint32_t)(half ? 8 : 16) * (uint32_t)p.RS);
+                        tma_load_2d(sbase, half ? &p.wmap8 : &p.wmap16, seg * p.SB * 4, row0, fullb);
+                    }
+                    // pull this stage's absmax lines into L2 ahead of the compute warps' loads
+                    if (lane < (half ? 8 : 16) && row0 + lane < p.N) {
+                        const float* a = p.absmax + (int64_t)(row0 + lane) * p.KB + seg * p.SB;
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+                    }
+                    __syncwarp();
+                    ++stage;
+                    if (++slot == p.NS) { slot = 0; parity ^= 1u; }
+                }
+            }
+        }
+        return;
+    }
+
+    // ----------------------------------- compute warps ------------------------------------------
+    lut_build<T>(lut_ptr, p.code16, warp, SG_COMPUTE_WARPS, lane);
+    // the table is complete for everybody after this barrier (compute warps only)
+    asm volatile("bar.sync 1, %0;" ::"n"(SG_COMPUTE_WARPS * 32) : "memory");
+    if (p.x_staged) mbar_wait(xbar, 0u, abort_flag, 3, -1);
+
+    const uint32_t window_lane = lut_base | (uint32_t)(lane << 2);
+    // A block this warp does not own (SB < 32) reads a valid block of the stage against all-zero
+    // activation fragments, so both blocks are always computed.
+    int off_a[BPW], blk[BPW];
+#pragma unroll
+    for (int bi = 0; bi < BPW; ++bi) {
+        blk[bi] = min(warp + bi * CW, p.SB - 1);
+        off_a[bi] = g * p.RS + blk[bi] * 32 + q * 8;
+    }
+    // absmax goes global -> registers, one stage ahead of its use (rows g and g+8 of the tile)
+    auto load_am = [&](float (&am)[BPW][2], int tile, int seg) {
+        const int row = r0 + tile * 16 + g;
+        const bool half = last_is_half && tile == ntiles - 1;
+#pragma unroll
+        for (int bi = 0; bi < BPW; ++bi) {
+            const float* a = p.absmax + (int64_t)row * p.KB + seg * p.SB + blk[bi];
+            am[bi][0] = row < p.N ? __ldg(a) : 0.0f;
+            am[bi][1] = (!half && row + 8 < p.N) ? __ldg(a + 8 * (int64_t)p.KB) : 0.0f;
+        }
+    };
+    float am_next[BPW][2];
+    if (ngroups > 0) load_am(am_next, 0, 0);
+
+    float acc[TG][NT][4];
+    int stage = 0, slot = 0;
+    uint32_t parity = 0;
+    for (int grp = 0; grp < ngroups; ++grp) {
+        const int nt_here = min(TG, ntiles - grp * TG);
+#pragma unroll
+        for (int j = 0; j < TG; ++j)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[j][nt][e] = 0.0f;
+
+        for (int seg = 0; seg < p.nseg; ++seg) {
+            // activation fragments of this warp's two blocks: 16 consecutive values of row m = g (+8)
+            uint32_t xf[BPW][NT][8];
+#pragma unroll
+            for (int bi = 0; bi < BPW; ++bi) {
+                const int kb = seg * p.SB + warp + bi * CW;
+                const bool live = (warp + bi * CW) < p.SB;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int m = g + nt * 8;
+                    uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
+                    if (live && m < p.M) {
+                        if (p.x_staged) {
+                            const uint4* src = reinterpret_cast<const uint4*>(xs + m * p.x_stride + ((kb * 64 + q * 16) << 1));
+                            v0 = src[0];
+                            v1 = src[1];
+                        } else {
+                            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x) +
+                                                                              (((int64_t)m * p.K + kb * 64 + q * 16) << 1));
+                            v0 = __ldg(src);
+                            v1 = __ldg(src + 1);
+                        }
+                    }
+                    xf[bi][nt][0] = v0.x; xf[bi][nt][1] = v0.y; xf[bi][nt][2] = v0.z; xf[bi][nt][3] = v0.w;
+                    xf[bi][nt][4] = v1.x; xf[bi][nt][5] = v1.y; xf[bi][nt][6] = v1.z; xf[bi][nt][7] = v1.w;
+                }
+            }
+
+#pragma unroll
+            for (int j = 0; j < TG; ++j) {
+                if (j < nt_here) {
+                    float am[BPW][2];
+#pragma unroll
+                    for (int bi = 0; bi < BPW; ++bi) { am[bi][0] = am_next[bi][0]; am[bi][1] = am_next[bi][1]; }
+                    {   // the stage after this one: next tile of the group, else next segment, else next group
+                        int j2 = j + 1, seg2 = seg, grp2 = grp;
+                        if (j2 >= nt_here) { j2 = 0; if (++seg2 >= p.nseg) { seg2 = 0; ++grp2; } }
+                        if (grp2 < ngroups) load_am(am_next, grp2 * TG + j2, seg2);
+                    }
+                    mbar_wait(full0 + slot * 8, parity, abort_flag, 1, stage);
+                    const uint8_t* const sb = ring + slot * p.stage_bytes;
+                    const bool half = last_is_half && (grp * TG + j) == ntiles - 1;   // rows 8..15 absent
+                    if (!half) block_set<T, NT, BPW, false>(sb, off_a, am, p.RS, window_lane, xf, acc[j]);
+                    else block_set<T, NT, BPW, true>(sb, off_a, am, p.RS, window_lane, xf, acc[j]);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty0 + slot * 8);
+                    ++stage;
+                    if (++slot == p.NS) { slot = 0; parity ^= 1u; }
+                }
+            }
+        }
+
+        // ---- end of a group: the 16 partial sums of every output meet in shared memory --------
+        // layout part[warp][j][m][16 rows]
+        const int Mc = p.M;
+        float* const mine = part + warp * (TG * Mc * 16);
+#pragma unroll
+        for (int j = 0; j < TG; ++j) {
+            if (j < nt_here) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int m = nt * 8 + 2 * q;
+                    if (m < Mc) {
+                        mine[(j * Mc + m) * 16 + g] = acc[j][nt][0];
+                        mine[(j * Mc + m) * 16 + g + 8] = acc[j][nt][2];
+                    }
+                    if (m + 1 < Mc) {
+                        mine[(j * Mc + m + 1) * 16 + g] = acc[j][nt][1];
+                        mine[(j * Mc + m + 1) * 16 + g + 8] = acc[j][nt][3];
+                    }
+                }
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(SG_COMPUTE_WARPS * 32) : "memory");
+        const int outputs = nt_here * Mc * 16;
+        for (int o = tid; o < outputs; o += SG_COMPUTE_WARPS * 32) {
+            const int row = o & 15;
+            const int jm = o >> 4;           // j * Mc + m
+            const int j = jm / Mc;
+            const int m = jm - j * Mc;
+            const int grow = r0 + (grp * TG + j) * 16 + row;
+            if (grow < r1) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < SG_COMPUTE_WARPS; ++w) sum += part[w * (TG * Mc * 16) + o];
+                if (p.bias) sum += Elem<T>::to_f32(static_cast<const T*>(p.bias)[grow]);
+                static_cast<T*>(p.y)[(int64_t)m * p.N + grow] = Elem<T>::from_f32(sum);
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(SG_COMPUTE_WARPS * 32) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+
+template <typename T, int NT, int TG, int CW>
+static int launch_staged(const StagedParams& p, int grid, cudaStream_t stream) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 64 && !configured[dev]) {
+        NF4_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<T, NT, TG, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM));
+        configured[dev] = true;
+    }
+    gemv_staged_kernel<T, NT, TG, CW><<<grid, (CW + 1) * 32, GEMV_SMEM, stream>>>(p);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+// ---- tensor maps ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+struct MapSet { CUtensorMap w16, w8, a16, a8; };
+
+// One set of maps per (weight pointer, absmax pointer, N, K, SB); a map encodes only address and
+// geometry, so it stays valid when the buffer's contents change.
+static int get_maps(const uint8_t* packed, const float* absmax, int N, int K, int SB, const MapSet** out) {
+    typedef std::tuple<const void*, const void*, int, int, int, int> Key;
+    static std::map<Key, MapSet> cache;
+    static std::mutex mu;
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key(packed, absmax, N, K, SB, dev);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        EncodeTiledFn enc = encode_fn();
+        NF4_REQUIRE(enc, NF4_ERR_CUDA, "gemv: cuTensorMapEncodeTiled is not available from this driver");
+        if (cache.size() > 4096) cache.clear();
+        MapSet ms;
+        const int KB = K / 64;
+        const cuuint32_t estr[2] = {1, 1};
+        for (int i = 0; i < 2; ++i) {
+            const cuuint32_t rows = i == 0 ? 16 : 8;
+            const cuuint64_t wdim[2] = {(cuuint64_t)(K / 16), (cuuint64_t)N};      // uint64 elements per row
+            const cuuint64_t wstr[1] = {(cuuint64_t)(K / 2)};
+            const cuuint32_t wbox[2] = {(cuuint32_t)(SB * 4 + 4), rows};
+            CUresult r = enc(i == 0 ? &ms.w16 : &ms.w8, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t*>(packed), wdim, wstr,
+                             wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            NF4_REQUIRE(r == CUDA_SUCCESS, NF4_ERR_CUDA, "gemv: cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
+            const cuuint64_t adim[2] = {(cuuint64_t)KB, (cuuint64_t)N};
+            const cuuint64_t astr[1] = {(cuuint64_t)KB * 4};
+            const cuuint32_t abox[2] = {(cuuint32_t)(SB + 4), rows};
+            r = enc(i == 0 ? &ms.a16 : &ms.a8, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(absmax), adim, astr, abox,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            NF4_REQUIRE(r == CUDA_SUCCESS, NF4_ERR_CUDA, "gemv: cuTensorMapEncodeTiled(absmax) failed with %d", (int)r);
+        }
+        it = cache.emplace(key, ms).first;
+    }
+    *out = &it->second;
+    return NF4_OK;
+}
+
+// Returns NF4_OK after launching, an error code, or -1 when the shape does not fit this kernel (the
+// caller then takes the direct-load kernel).
+template <typename T>
+int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16, int N,
+                    const void* bias, void* y, cudaStream_t stream) {
+    const int KB = K / 64;
+    if (KB % 4 != 0) return -1;
+    if (reinterpret_cast<uintptr_t>(packed) % 16 || reinterpret_cast<uintptr_t>(absmax) % 16 ||
+        reinterpret_cast<uintptr_t>(x) % 16)
+        return -1;
+    int SB = 0;
+    for (int c = 32; c >= 8; c -= 4)
+        if (KB % c == 0) { SB = c; break; }
+    if (SB == 0) return -1;
+    if (const char* env = getenv("NF4_GEMV_SB")) {   // tuning override: blocks per stage
+        const int v = atoi(env);
+        if (v >= 8 && v <= 32 && v % 4 == 0 && KB % v == 0) SB = v;
+    }
+    const int NT = M <= 8 ? 1 : 2;
+    const int sms = sm_count();
+    const int H = (N + 7) / 8;
+    int grid = sms;
+    if (grid > (H + 1) / 2) grid = (H + 1) / 2;
+    const int tiles = ((H + grid - 1) / grid + 1) / 2;
+    int TG = NT == 1 ? 4 : 2;
+    while (TG > 1 && TG / 2 >= tiles) TG /= 2;
+    if (const char* env = getenv("NF4_GEMV_TG")) {
+        const int v = atoi(env);
+        if (v == 1 || v == 2 || (v == 4 && NT == 1)) TG = v;
+    }
+
+    StagedParams p;
+    const MapSet* ms = nullptr;
+    if (int rc = get_maps(packed, absmax, N, K, SB, &ms)) return rc;
+    p.wmap16 = ms->w16; p.wmap8 = ms->w8; p.amap16 = ms->a16; p.amap8 = ms->a8;
+    p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.y = y;
+    p.M = M; p.N = N; p.K = K; p.KB = KB; p.SB = SB; p.nseg = KB / SB;
+    p.RS = SB * 32 + 32;
+    p.AS = SB * 4 + 16;
+    p.stage_bytes = 16 * p.RS;   // a multiple of 512 bytes
+    p.x_stride = 2 * K + 16;
+    // Shared-memory map.  The dynamic region starts ~1 KB into the shared window, the table takes
+    // the 64 KB aligned window [64K, 128K); below it: barriers, partial sums, staged activations;
+    // above it: the ring (every stage and both boxes inside it start on a 128-byte boundary).
+    const int low_cap = LUT_WINDOW - 2048;           // leaves room for the window's start offset
+    p.off_bars = 0;
+    p.off_part = 256;
+    int CW = 16;
+    if (const char* env = getenv("NF4_GEMV_CW")) {
+        const int v = atoi(env);
+        if (v == 8 || v == 16) CW = v;
+    }
+    const int part_bytes = CW * TG * M * 16 * 4;
+    p.off_x = (p.off_part + part_bytes + 127) & ~127;
+    if (p.off_x > low_cap) return -1;
+    p.x_staged = ((int64_t)p.off_x + (int64_t)M * p.x_stride <= low_cap) ? 1 : 0;
+    const int ring_cap = GEMV_SMEM - 2 * LUT_WINDOW;   // the window ends at most 128 KB into the region
+    int NS = ring_cap / p.stage_bytes;
+    if (NS > SG_MAX_STAGES) NS = SG_MAX_STAGES;
+    if (NS < 2) return -1;
+    if (const char* env = getenv("NF4_GEMV_NS")) {   // tuning override: ring depth
+        const int v = atoi(env);
+        if (v >= 2 && v <= NS) NS = v;
+    }
+    p.NS = NS;
+
+#define NF4_SG(NT_, TG_)                                                        \
+    do {                                                                        \
+        if (CW == 8) return launch_staged<T, NT_, TG_, 8>(p, grid, stream);     \
+        return launch_staged<T, NT_, TG_, 16>(p, grid, stream);                 \
+    } while (0)
+    if (NT == 1) {
+        if (TG == 4) NF4_SG(1, 4);
+        if (TG == 2) NF4_SG(1, 2);
+        NF4_SG(1, 1);
+    } else {
+        if (TG == 2) NF4_SG(2, 2);
+        NF4_SG(2, 1);
+    }
+#undef NF4_SG
+}
+
+template int gemv_staged_try<__nv_bfloat16>(const void*, int, int, const uint8_t*, const float*, const float*, int,
+                                            const void*, void*, cudaStream_t);
+template int gemv_staged_try<__half>(const void*, int, int, const uint8_t*, const float*, const float*, int, const void*,
+                                     void*, cudaStream_t);
+
+}  // namespace nf4
+
+using namespace nf4;
+
+extern "C" int nf4_b200_device_error(unsigned int* host_out4) {
+    NF4_REQUIRE(host_out4, NF4_ERR_ARG, "device_error: null pointer");
+    NF4_CUDA_TRY(cudaMemcpyFromSymbol(host_out4, g_gemv_error, sizeof(unsigned int) * 4));
+    return NF4_OK;
+}

@@ -32,6 +32,7 @@ SIGNATURES = {
                                _c_ptr, _c_i64, _c_ptr]),
     "nf4_b200_linear_generic": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr,
                                          _c_ptr, _c_int, _c_ptr]),
+    "nf4_b200_device_error": (_c_int, [_c_ptr]),
 }
 
 _lib = None
@@ -63,6 +64,13 @@ def last_error() -> str:
     buf = ctypes.create_string_buffer(512)
     load().nf4_b200_last_error(buf, 512)
     return buf.value.decode("utf-8", "replace")
+
+
+def device_error():
+    """(code, block, stage, count) of the first in-kernel wait that ran out; synchronises."""
+    out = (ctypes.c_uint * 4)()
+    check(load().nf4_b200_device_error(out), "nf4_b200_device_error")
+    return tuple(out)
 
 
 def check(status: int, what: str) -> None:

@@ -99,8 +99,19 @@ def dequantize(packed: np.ndarray, absmax: np.ndarray, code16: np.ndarray, numel
     return res
 
 
-def linear_bf16(x_bits: np.ndarray, packed, absmax, code16, N: int, K: int, blocksize: int = 64, bias_bits=None):
-    """x_bits: uint16 [M,K] bf16 bit patterns.  Returns uint16 [M,N] bf16 bit patterns."""
+GEMM_MODE, GEMV_MODE = 0, 1
+
+
+def linear_mode_for(M: int) -> int:
+    """The regime the library takes for M activation rows (fused GEMV up to 16 rows)."""
+    return GEMV_MODE if M <= 16 else GEMM_MODE
+
+
+def linear_bf16(x_bits: np.ndarray, packed, absmax, code16, N: int, K: int, blocksize: int = 64, bias_bits=None,
+                mode=None):
+    """x_bits: uint16 [M,K] bf16 bit patterns.  Returns uint16 [M,N] bf16 bit patterns.
+    mode: GEMM_MODE (weights rounded to bf16, then matmul), GEMV_MODE (levels rounded to bf16, block
+    sums scaled in fp32); default = the regime the library takes for this M."""
     x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16).reshape(-1, K)
     M = x_bits.shape[0]
     code16 = np.ascontiguousarray(code16, dtype=np.float32)
@@ -110,7 +121,8 @@ def linear_bf16(x_bits: np.ndarray, packed, absmax, code16, N: int, K: int, bloc
     b = None if bias_bits is None else np.ascontiguousarray(bias_bits, dtype=np.uint16)
     lib().nf4_oracle_linear_bf16(_p(x_bits), ctypes.c_int64(M), ctypes.c_int64(K), _p(packed), _p(absmax),
                                  _p(code16), ctypes.c_int64(N), ctypes.c_int(blocksize),
-                                 _p(b) if b is not None else None, _p(y))
+                                 _p(b) if b is not None else None, _p(y),
+                                 ctypes.c_int(linear_mode_for(M) if mode is None else mode))
     return y
 
 

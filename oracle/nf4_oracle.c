@@ -20,8 +20,9 @@
  *   4. index = argmin_i |v - code[i]| evaluated in fp32, the lower index wins a tie;
  *   5. byte j = (index[2j] << 4) | index[2j+1]; an odd tail leaves the low nibble 0;
  *   6. dequant: code[index] * absmax[b] in fp32, one round-to-nearest-even to the output type;
- *   7. linear: y[m][n] = round_bf16( sum_k x[m][k] * Wdeq[n][k] + bias[n] ), Wdeq already
- *      rounded to x's type (what a dequantize-then-matmul path multiplies with).
+ *   7. linear: y[m][n] = round_bf16( sum_k x[m][k] * Wdeq[n][k] + bias[n] ) in one of two modes
+ *      (see nf4_oracle_linear_bf16): Wdeq rounded to x's type first ("dequantize then matmul"),
+ *      or levels rounded to x's type and scaled per block in fp32 ("fused GEMV").
  *
  * PARITY UNPINNED: the reference holds no golden bytes for this path and bitsandbytes
  * cannot be run here; steps 3-5 are decisions of this restatement.
@@ -140,10 +141,20 @@ void nf4_oracle_dequantize_bf16(const uint8_t* packed, const float* absmax, cons
 }
 
 /* step 7 for bf16 activations: x [M,K], packed W [N,K] row-major flattened, y [M,N] bf16 bits.
- * The dequantised row is rounded to bf16 first; accumulation is fp32 in 8 lanes. */
+ * The reference's library has two regimes and the oracle restates both:
+ *   mode 0 "dequantize then matmul" (many activation rows): the dequantised weight is rounded to
+ *          bf16 first (step 6), products are accumulated in fp32;
+ *   mode 1 "fused GEMV" (few activation rows): the 16 levels are rounded to bf16, a 64-block
+ *          contributes absmax * sum_k(x[k] * level_bf16[idx[k]]) with the inner sum and the
+ *          scaling in fp32 -- no per-weight rounding of the product.
+ * Both round once to bf16 at the end.  The two differ by the bf16 rounding noise of the weights
+ * (unit roundoff 2^-8 per weight), which at K >= 4096 exceeds atol 1e-2; a kernel is therefore
+ * checked against the mode it implements. */
 void nf4_oracle_linear_bf16(const uint16_t* x, int64_t M, int64_t K, const uint8_t* packed,
                             const float* absmax, const float* code16, int64_t N, int blocksize,
-                            const uint16_t* bias, uint16_t* y) {
+                            const uint16_t* bias, uint16_t* y, int mode) {
+    float code_r[16];
+    for (int i = 0; i < 16; ++i) code_r[i] = bf16_bits_to_f32(f32_to_bf16_bits(code16[i]));
 #pragma omp parallel
     {
         float wrow[K];
@@ -153,16 +164,33 @@ void nf4_oracle_linear_bf16(const uint16_t* x, int64_t M, int64_t K, const uint8
                 int64_t i = n * K + k;
                 uint8_t byte = packed[i >> 1];
                 int idx = (i & 1) ? (byte & 15) : (byte >> 4);
-                wrow[k] = bf16_bits_to_f32(f32_to_bf16_bits(code16[idx] * absmax[i / blocksize]));
+                if (mode == 0) wrow[k] = bf16_bits_to_f32(f32_to_bf16_bits(code16[idx] * absmax[i / blocksize]));
+                else wrow[k] = code_r[idx];
             }
             for (int64_t m = 0; m < M; ++m) {
                 const uint16_t* xr = x + m * K;
-                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                int64_t k = 0;
-                for (; k + 8 <= K; k += 8)
-                    for (int j = 0; j < 8; ++j) acc[j] += bf16_bits_to_f32(xr[k + j]) * wrow[k + j];
-                float s = ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
-                for (; k < K; ++k) s += bf16_bits_to_f32(xr[k]) * wrow[k];
+                float s;
+                if (mode == 0) {
+                    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    int64_t k = 0;
+                    for (; k + 8 <= K; k += 8)
+                        for (int j = 0; j < 8; ++j) acc[j] += bf16_bits_to_f32(xr[k + j]) * wrow[k + j];
+                    s = ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
+                    for (; k < K; ++k) s += bf16_bits_to_f32(xr[k]) * wrow[k];
+                } else {
+                    s = 0.0f;
+                    int64_t k = 0;
+                    while (k < K) {
+                        /* one run of elements that share an absmax (rows need not start on a block) */
+                        int64_t i0 = n * K + k;
+                        int64_t b = i0 / blocksize;
+                        int64_t kend = k + ((b + 1) * blocksize - i0);
+                        if (kend > K) kend = K;
+                        float part = 0.0f;
+                        for (; k < kend; ++k) part += bf16_bits_to_f32(xr[k]) * wrow[k];
+                        s += part * absmax[b];
+                    }
+                }
                 if (bias) s += bf16_bits_to_f32(bias[n]);
                 y[m * N + n] = f32_to_bf16_bits(s);
             }

@@ -16,17 +16,24 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 1.6e-2, 1e-2
 
 
-def _oracle_linear(x_cpu, packed_np, absmax_np, code, N, K, bias_cpu=None):
+# The M > 16 entry point currently runs the fused-GEMV kernel once per slab of 16 activation rows,
+# so its results follow the oracle's GEMV regime.
+GEMM_ORACLE_MODE = oracle.GEMV_MODE
+
+
+def _oracle_linear(x_cpu, packed_np, absmax_np, code, N, K, bias_cpu=None, mode=None, blocksize=64):
     if x_cpu.dtype == torch.bfloat16:
-        y = oracle.linear_bf16(bf16_bits(x_cpu), packed_np, absmax_np, code, N, K, 64,
-                               None if bias_cpu is None else bf16_bits(bias_cpu))
+        if mode is None:
+            mode = oracle.GEMV_MODE if x_cpu.shape[0] <= 16 else GEMM_ORACLE_MODE
+        y = oracle.linear_bf16(bf16_bits(x_cpu), packed_np, absmax_np, code, N, K, blocksize,
+                               None if bias_cpu is None else bf16_bits(bias_cpu), mode=mode)
         return bits_to_bf16(y).float()
-    y = oracle.linear_f32(x_cpu.float().numpy(), packed_np, absmax_np, code, N, K, 64,
+    y = oracle.linear_f32(x_cpu.float().numpy(), packed_np, absmax_np, code, N, K, blocksize,
                           None if bias_cpu is None else bias_cpu.float().numpy())
     return torch.from_numpy(y)
 
 
-def _check(x_cpu, w_cpu, code, bias_cpu=None, blocksize=64):
+def _check(x_cpu, w_cpu, code, bias_cpu=None, blocksize=64, mode=None):
     import nf4_b200
 
     N, K = w_cpu.shape
@@ -36,13 +43,7 @@ def _check(x_cpu, w_cpu, code, bias_cpu=None, blocksize=64):
     torch.cuda.synchronize()
     assert y.shape == (*x_cpu.shape[:-1], N) and y.dtype == x_cpu.dtype
     p_np, a_np = packed.cpu().numpy(), qs.absmax.cpu().numpy()
-    if blocksize == 64:
-        ref = _oracle_linear(x_cpu.reshape(-1, K), p_np, a_np, code, N, K, bias_cpu)
-    else:
-        wd = oracle.dequantize(p_np, a_np, code, N * K, blocksize, out="f32").reshape(N, K)
-        ref = torch.from_numpy(x_cpu.float().numpy().reshape(-1, K).astype(np.float64) @ wd.astype(np.float64).T).float()
-        if bias_cpu is not None:
-            ref += bias_cpu.float()
+    ref = _oracle_linear(x_cpu.reshape(-1, K), p_np, a_np, code, N, K, bias_cpu, mode=mode, blocksize=blocksize)
     got = y.float().cpu().reshape(-1, N)
     torch.testing.assert_close(got, ref, rtol=RTOL, atol=ATOL)
     return y
@@ -71,10 +72,37 @@ def test_gemv_shapes(nf4_code_np, M, N, K):
 @pytest.mark.parametrize("plan", ["1,0", "1,2", "2,1", "2,4", "4,0", "4,3"])
 def test_gemv_every_plan(nf4_code_np, plan, monkeypatch):
     """Forces each (rows-per-warp, K-split) variant of the GEMV on the same problem."""
+    monkeypatch.setenv("NF4_GEMV_KERNEL", "direct")
     monkeypatch.setenv("NF4_GEMV_PLAN", plan)
     w = seeded_weight((1500, 2048), 17)
     for M in (1, 5, 12):
         _check(seeded_act((M, 2048), M + 100), w, nf4_code_np)
+
+
+@pytest.mark.parametrize("kernel", ["direct", "staged"])
+@pytest.mark.parametrize("M", [1, 3, 8, 11, 16])
+@pytest.mark.parametrize("N,K", [(14336, 4096), (2000, 2048), (515, 7168), (64, 512), (5, 1024), (4096, 3584)])
+def test_gemv_both_kernels(nf4_code_np, kernel, M, N, K, monkeypatch):
+    """The staged (bulk-copy ring) and the direct-load GEMV kernels on the same problems, with a
+    row count that is not a multiple of the tile and K values with 16, 28 and 32 blocks per stage."""
+    from nf4_b200 import _lib
+
+    monkeypatch.setenv("NF4_GEMV_KERNEL", kernel)
+    w = seeded_weight((N, K), N + 3 * K)
+    _check(seeded_act((M, K), M), w, nf4_code_np, bias_cpu=seeded_act((N,), 2))
+    assert _lib.device_error()[0] == 0
+
+
+@pytest.mark.parametrize("tg", ["1", "2", "4"])
+def test_gemv_staged_group_sizes(nf4_code_np, tg, monkeypatch):
+    from nf4_b200 import _lib
+
+    monkeypatch.setenv("NF4_GEMV_KERNEL", "staged")
+    monkeypatch.setenv("NF4_GEMV_TG", tg)
+    w = seeded_weight((128256 // 8, 4096), 5)     # 108 rows per CTA: several groups, ragged last tile
+    for M in (1, 6, 16):
+        _check(seeded_act((M, 4096), M + 50), w, nf4_code_np)
+    assert _lib.device_error()[0] == 0
 
 
 def test_gemv_bias_fp16_and_batch_dims(nf4_code_np):
@@ -112,12 +140,12 @@ def test_generic_kernel_ragged_shapes(nf4_code_np, dtype, M, N, K):
     w = seeded_weight((N, K), N * K, std=0.3, dtype=dtype)
     x = seeded_act((M, K), M + K, dtype=dtype)
     b = seeded_act((N,), 1, dtype=dtype)
-    _check(x, w, nf4_code_np, bias_cpu=b)
+    _check(x, w, nf4_code_np, bias_cpu=b, mode=oracle.GEMV_MODE)   # the generic kernel has the GEMV numerics
 
 
 def test_other_blocksize_uses_generic(nf4_code_np):
     w = seeded_weight((128, 512), 8)
-    _check(seeded_act((4, 512), 2), w, nf4_code_np, blocksize=128)
+    _check(seeded_act((4, 512), 2), w, nf4_code_np, blocksize=128, mode=oracle.GEMV_MODE)
 
 
 def test_linearity_at_full_size(nf4_code_np):
