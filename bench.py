@@ -1,0 +1,389 @@
+"""Benchmark of the NF4 W4A16 decode path.
+
+    python bench.py --gpus N --steps K --warmup W          (N > 1: launched under torch.distributed.run)
+    python bench.py --impl reference ...                   the CPU restatement of the same path, host cores
+    python bench.py --kernel gemv --N 14336 --K 4096 --M 1 one kernel in isolation (used for ncu captures)
+
+Workload (synthetic, random-init, seeded): N = 1 -> a Llama-3-8B-shaped NF4 decoder, batch 1, a
+512-token random prompt in the KV cache, greedy decode; a "step" is one decode step (one token per
+batch row through all 225 quantized linears + attention over the cache).  N > 1 -> the
+Llama-3-70B-shaped decoder, batch 16, 1024-token prompt, tensor-parallel over the N GPUs (strong
+scaling: the model is fixed).  `value` is tokens/s with the token ids staying on the device;
+`e2e` feeds every step's token ids from pinned host memory and reads the sampled ids back.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "lightning-thunder_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "NF4 W4A16 decode tok/s (Llama-3-8B shape); dequant-GEMV HBM GB/s vs 8 TB/s"
+UNIT = "tok/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for j, n in enumerate(names) if any(len(r) >= 7 and r[3 + j].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle's linears on the host cores
+# --------------------------------------------------------------------------------------------
+
+def cpu_decode_sample(cfg_name: str, batch: int, reps: int):
+    """Times the quantized linears of ONE decoder layer (QKV, attention output, gate+up, down) at
+    `batch` activation rows with the CPU oracle (OpenMP, all host threads), `reps` times, and scales
+    to a whole model: tok/s = batch / (n_layers * t_layer + t_head_estimate).  Weights come from the
+    oracle's own quantizer on seeded N(0, 0.02) data."""
+    import numpy as np
+
+    import oracle
+    from nf4_b200.codebook import NF4_LEVELS
+    from nf4_b200.decoder import LLAMA3_8B, LLAMA3_70B
+
+    cfg = LLAMA3_70B if "70b" in cfg_name else LLAMA3_8B
+    code = np.array(NF4_LEVELS, np.float32)
+    rng = np.random.default_rng(0)
+    D, F = cfg.d_model, cfg.ffn
+    shapes = [((cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim, D), (D, cfg.n_heads * cfg.head_dim), (2 * F, D), (D, F)]
+    mats = []
+    for (N, K) in shapes:
+        w = (rng.standard_normal((N, K), dtype=np.float32) * 0.02)
+        packed, absmax = oracle.quantize(oracle.f32_to_bf16_bits(w), code, 64)
+        x = oracle.f32_to_bf16_bits(rng.standard_normal((batch, K), dtype=np.float32))
+        mats.append((x, packed, absmax, N, K))
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for (x, packed, absmax, N, K) in mats:
+            oracle.linear_bf16(x, packed, absmax, code, N, K, 64, mode=oracle.GEMV_MODE)
+        times.append(time.perf_counter() - t0)
+    t_layer = statistics.median(times)
+    layer_weights = sum(N * K for (_, _, _, N, K) in mats)
+    t_head = t_layer * (cfg.vocab * D) / layer_weights
+    tok_s = batch / (cfg.n_layers * t_layer + t_head)
+    return tok_s, t_layer, os.cpu_count()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    workload = args.workload or ("llama3-8b" if args.gpus == 1 else "llama3-70b")
+    batch = 1 if "8b" in workload else 16
+    tok_s, t_layer, cores = cpu_decode_sample(workload, batch, max(1, args.steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000.0 * batch / tok_s, "higher_is_better": True,
+        "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{workload}-shape NF4 decode, batch {batch}", "l2": "weights larger than any cache"},
+        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"the 4 quantized linears of one decoder layer at M={batch}, median of {max(1, args.steps)} "
+                                   f"passes ({t_layer * 1e3:.1f} ms each), scaled to all layers + output head"},
+        "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------------
+# single-kernel mode (profiling driver)
+# --------------------------------------------------------------------------------------------
+
+def run_kernel(args):
+    import ctypes
+
+    import torch
+
+    import nf4_b200
+    from nf4_b200 import _lib
+
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    N, K, M = args.N, args.K, args.M
+    wbytes = N * K // 2 + N * K // 16
+    nbuf = args.nbuf or max(2, int(4 * 126e6 // wbytes) + 1)     # the rotating set is > 4x the L2
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ws = []
+    for _ in range(nbuf):
+        w = (torch.randn((N, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+        ws.append(nf4_b200.quantize_4bit(w))
+        del w
+    x = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
+    y = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+
+    def launch_all():
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for p, qs in ws:
+            if args.kernel == "gemv":
+                rc = lib.nf4_b200_linear(x.data_ptr(), M, K, p.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N, 64,
+                                         None, y.data_ptr(), _lib.NF4_BF16, None, 0, st)
+            elif args.kernel == "dequantize":
+                rc = lib.nf4_b200_dequantize(p.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N * K, 64,
+                                             deq.data_ptr(), _lib.NF4_BF16, st)
+            else:
+                rc = lib.nf4_b200_quantize(deq.data_ptr(), N * K, _lib.NF4_BF16, 64, qs.code.data_ptr(), p.data_ptr(),
+                                           qs.absmax.data_ptr(), st)
+            _lib.check(rc, args.kernel)
+
+    deq = torch.empty((N, K), device="cuda", dtype=torch.bfloat16) if args.kernel != "gemv" else None
+    if deq is not None:
+        deq.copy_(nf4_b200.dequantize_4bit(*ws[0]))
+    for _ in range(max(1, args.warmup)):
+        launch_all()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ts = []
+    for _ in range(max(1, args.steps)):
+        e0.record()
+        launch_all()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / nbuf)
+    us = statistics.median(ts)
+    if args.kernel == "gemv":
+        alg = wbytes + 2 * M * K + 2 * M * N
+    else:
+        alg = 2 * N * K + wbytes
+    peaks, src = measured_peaks()
+    print(json.dumps({"kernel": args.kernel, "N": N, "K": K, "M": M, "us_per_launch": us, "algorithmic_bytes": alg,
+                      "GBps": alg / us / 1e3, "frac_of_" + src: alg / us / 1e3 / peaks["hbm_gbs"], "buffers": nbuf}))
+
+
+# --------------------------------------------------------------------------------------------
+# the decode benchmark
+# --------------------------------------------------------------------------------------------
+
+def run_decode(args):
+    import torch
+
+    from nf4_b200 import _lib
+    from nf4_b200.decoder import LLAMA3_8B, LLAMA3_70B, NF4Decoder, tiny_config
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+        group = dist.group.WORLD
+
+    workload = args.workload or ("llama3-8b" if world == 1 else "llama3-70b")
+    if workload == "llama3-8b":
+        cfg, batch, prompt_len, new_tokens = LLAMA3_8B, 1, 512, 128
+    elif workload == "llama3-70b":
+        cfg, batch, prompt_len, new_tokens = LLAMA3_70B, 16, 1024, 256
+    else:
+        cfg, batch, prompt_len, new_tokens = tiny_config(), 1, 16, 16
+    if args.prompt is not None:
+        prompt_len = args.prompt
+    steps, warmup = args.steps, max(3, args.warmup)
+    max_seq = prompt_len + warmup + 2 * steps + 8
+
+    t_build = time.perf_counter()
+    dec = NF4Decoder(cfg, batch=batch, max_seq=max_seq, device=dev, seed=1, tp_rank=rank, tp_size=world, group=group)
+    torch.cuda.synchronize()
+    t_build = time.perf_counter() - t_build
+
+    g_host = dec.capture(feed_back=False)
+    g_dev = dec.capture(feed_back=True)
+    launches = dec.launches_per_step
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # prompt -> KV cache, one token per step (the same decode path; no separate prefill kernel is timed)
+    gen = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=gen)
+    prompt_dev = prompt.to(dev)
+    dec.reset()
+    dec.graph = g_host
+    for t in range(prompt_len):
+        dec.ids_in.copy_(prompt_dev[:, t])
+        dec.run_step()
+    torch.cuda.synchronize()
+
+    # ---- device-resident greedy loop: `value`
+    dec.graph = g_dev
+    dec.ids_in.copy_(dec.ids_out)
+    for _ in range(warmup):
+        dec.run_step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        dec.run_step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    tok_s = steps * batch / (ms / 1e3)
+
+    # ---- end to end: every step the ids come from pinned host memory and the sampled ids go back
+    dec.graph = g_host
+    ids_host = torch.empty((batch,), dtype=torch.int64).pin_memory()
+    out_host = torch.empty((batch,), dtype=torch.int64).pin_memory()
+    ids_host.copy_(dec.ids_out.cpu())
+    barrier()
+    w0 = time.perf_counter()
+    for _ in range(steps):
+        dec.ids_in.copy_(ids_host, non_blocking=True)
+        dec.run_step()
+        out_host.copy_(dec.ids_out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        ids_host.copy_(out_host)
+    barrier()
+    e2e_s = time.perf_counter() - w0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_tok_s = steps * batch / e2e_s
+
+    # ---- roofline of the dominant kernel (the fused dequant-GEMV): one more decode step, not
+    # captured, with an event pair around every GEMV launch on the launching stream
+    dec.graph = None
+    ev = []
+    orig_linear = dec._linear
+
+    def timed_linear(x, w, y, residual=None, stream=None):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        orig_linear(x, w, y, residual=residual, stream=stream)
+        b.record()
+        ev.append((a, b, w.nbytes() + 2 * x.shape[0] * (w.K + w.N)))
+
+    dec._linear = timed_linear
+    dec.ids_in.copy_(dec.ids_out)
+    dec.step()
+    torch.cuda.synchronize()
+    dec._linear = orig_linear
+    gemv_us = [a.elapsed_time(b) * 1e3 for a, b, _ in ev]
+    gemv_bytes = [n for _, _, n in ev]
+    peaks, src = measured_peaks()
+    achieved = sum(gemv_bytes) / sum(gemv_us) / 1e3       # GB/s over all GEMV launches of a step
+    dev_err = _lib.device_error()
+
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+
+    cpu_tok_s, t_layer, cores = cpu_decode_sample(workload if workload != "tiny" else "llama3-8b", batch, 3)
+    step_bytes = dec.weight_bytes()
+    line = {
+        "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{cfg.name} NF4 decode, batch {batch}, {prompt_len}-token prompt in the KV cache, greedy",
+                   "parallelism": f"tp{world}", "global_batch": batch, "context": prompt_len,
+                   "l2": f"{step_bytes / 1e9:.2f} GB of weights stream per step per GPU (> L2), no flush needed",
+                   "blocksize": 64, "double_quant": False},
+        "clocks": clocks,
+        "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
+        "gpu_launches": launches * steps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "peak_source": src, "traffic": None,
+                     "kernel": "gemv_staged_kernel (fused NF4 dequant-GEMV)", "launches_per_step": len(ev),
+                     "avg_launch_us": sum(gemv_us) / len(gemv_us), "algorithmic_bytes_per_launch": sum(gemv_bytes) / len(gemv_bytes),
+                     "frac_of_8TBps": achieved / 8000.0,
+                     "whole_step_GBps": step_bytes / (ms / steps / 1e3) / 1e9},
+        "cpu_baseline": {"value": cpu_tok_s, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"the 4 quantized linears of one decoder layer at M={batch} on the CPU oracle, median of 3 "
+                                   f"passes ({t_layer * 1e3:.1f} ms each), scaled to all layers + output head"},
+        "build_s": t_build, "device_error": list(dev_err),
+    }
+    print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=[None, "llama3-8b", "llama3-70b", "tiny"])
+    ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
+    ap.add_argument("--kernel", default=None, choices=[None, "gemv", "quantize", "dequantize"])
+    ap.add_argument("--N", type=int, default=14336)
+    ap.add_argument("--K", type=int, default=4096)
+    ap.add_argument("--M", type=int, default=1)
+    ap.add_argument("--nbuf", type=int, default=None)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.kernel:
+        run_kernel(args)
+    else:
+        run_decode(args)
+
+
+if __name__ == "__main__":
+    main()

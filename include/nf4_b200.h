@@ -89,6 +89,41 @@ int nf4_b200_linear_generic(const void* x, int64_t M, int64_t K, const uint8_t* 
                             int dtype, void* stream);
 
 /*
+ * nf4_b200_gemv with one more epilogue term: y = x . dequant(W)^T + bias + residual, residual [M,N]
+ * of `dtype` (may be NULL, may alias y).  The reference has no fused form; it is what a decode step
+ * needs after the attention-output and MLP-down projections (thunder/tests/llama2_model.py:187-190).
+ */
+int nf4_b200_gemv_fused(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                        const float* code16, int64_t N, const void* bias, const void* residual, void* y, int dtype,
+                        void* stream);
+
+/*
+ * Decode-step glue kernels (bf16 tensors, fp32 arithmetic).  In the reference these ops are lowered
+ * by Thunder's executors from the model's trace (RMSNorm, rotary embedding, attention, SwiGLU:
+ * thunder/tests/llama2_model.py:20-40, 57-126, 142-190); here they are single launches so that one
+ * decode step of a Llama-shaped model is a short, capturable chain around the NF4 linears.
+ */
+/* y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * w[:] */
+int nf4_b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int64_t D, float eps, void* stream);
+/* Rotary embedding (interleaved pairs, base theta) of the q and k parts of qkv [B, (Hq+2*Hkv)*Dh] at
+ * positions[B]; q goes to q_out [B, Hq*Dh], rotated k and v go to the caches [B, Hkv, S_max, Dh]. */
+int nf4_b200_rope_append(const void* qkv, const int* positions, void* q_out, void* k_cache, void* v_cache,
+                         int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, float theta, void* stream);
+/* Single-query grouped attention over cache positions [0, positions[b]]; out [B, Hq*Dh].  Dh = 128.
+ * workspace: nf4_b200_attn_decode_workspace_bytes(B, Hq, nsplit) bytes. */
+int64_t nf4_b200_attn_decode_workspace_bytes(int64_t B, int Hq, int nsplit);
+int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* positions, void* out,
+                         void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit, void* stream);
+/* h[r,i] = silu(gate_up[r,i]) * gate_up[r,F+i], gate_up [rows, 2F] */
+int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, void* stream);
+/* y = a + b (numel even) */
+int nf4_b200_add(const void* a, const void* b, void* y, int64_t numel, void* stream);
+/* y[r,:] = table[ids[r],:] */
+int nf4_b200_embed(const int64_t* ids, const void* table, void* y, int64_t rows, int64_t D, int64_t vocab, void* stream);
+/* ids[r] = argmax_v logits[r,v], the first maximum wins */
+int nf4_b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t V, void* stream);
+
+/*
  * Status word of the kernels that wait on in-kernel barriers (the staged GEMV).  Copies 4 words to
  * host memory: [0] first error code (0 = none; 1/2/3 = a bounded wait on a full/empty/activation
  * barrier ran out, 4 = unexpected shared-memory window), [1] block index, [2] pipeline stage,

@@ -1,0 +1,340 @@
+// The small kernels that sit between the NF4 linears in a Llama-shaped decode step (bf16
+// activations, fp32 arithmetic): RMSNorm, rotary embedding + KV-cache append, single-query
+// grouped attention over the cache, SiLU(gate)*up, embedding lookup and greedy argmax.  They exist
+// so that a decode step is a short chain of launches that can be captured in one CUDA graph; the
+// reference leaves this glue to its trace executors (nvFuser / torch eager), which are not part
+// of this path.
+#include <cfloat>
+
+#include "nf4_common.cuh"
+
+namespace nf4 {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---- RMSNorm: y[r][:] = x[r][:] * rsqrt(mean(x^2) + eps) * w[:] ---------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                      bf16* __restrict__ y, int D, float eps) {
+    __shared__ float s_part[8];
+    const bf16* xr = x + (int64_t)blockIdx.x * D;
+    bf16* yr = y + (int64_t)blockIdx.x * D;
+    float ss = 0.0f;
+    for (int i = threadIdx.x * 2; i < D; i += 512) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + i));
+        ss += v.x * v.x + v.y * v.y;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += s_part[i];
+    const float r = rsqrtf(tot / (float)D + eps);
+    for (int i = threadIdx.x * 2; i < D; i += 512) {
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + i));
+        const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + i));
+        *reinterpret_cast<__nv_bfloat162*>(yr + i) = __floats2bfloat162_rn(v.x * r * g.x, v.y * r * g.y);
+    }
+}
+
+// ---- rotary embedding on q and k (interleaved pairs) + append k, v to the cache ---------------
+// qkv [B][(Hq + 2*Hkv) * Dh] as produced by the fused QKV linear; q_out [B][Hq*Dh];
+// k_cache / v_cache [B][Hkv][S_max][Dh]; positions[B] = index of the token being written.
+__global__ void rope_append_kernel(const bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                   bf16* __restrict__ q_out, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                   int Hq, int Hkv, int Dh, int S_max, float theta) {
+    const int b = blockIdx.y;
+    const int head = blockIdx.x;              // 0..Hq+2*Hkv-1
+    const int pos = positions[b];
+    const bf16* src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + head) * Dh;
+    const int i = threadIdx.x;                // pair index, Dh/2 threads
+    if (i >= Dh / 2) return;
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 2 * i));
+    if (head < Hq + Hkv) {
+        const float inv_freq = powf(theta, -2.0f * (float)i / (float)Dh);
+        float sn, cs;
+        sincosf((float)pos * inv_freq, &sn, &cs);
+        const __nv_bfloat162 r = __floats2bfloat162_rn(v.x * cs - v.y * sn, v.x * sn + v.y * cs);
+        if (head < Hq) {
+            *reinterpret_cast<__nv_bfloat162*>(q_out + ((int64_t)b * Hq + head) * Dh + 2 * i) = r;
+        } else {
+            const int h = head - Hq;
+            *reinterpret_cast<__nv_bfloat162*>(k_cache + (((int64_t)b * Hkv + h) * S_max + pos) * Dh + 2 * i) = r;
+        }
+    } else {
+        const int h = head - Hq - Hkv;
+        *reinterpret_cast<__nv_bfloat162*>(v_cache + (((int64_t)b * Hkv + h) * S_max + pos) * Dh + 2 * i) =
+            __floats2bfloat162_rn(v.x, v.y);
+    }
+}
+
+// ---- single-query attention over the cache, split along the sequence --------------------------
+// One CTA per (kv head, batch row, split).  Dh = 128: a lane owns 4 dims.  G = Hq/Hkv query heads
+// share the K/V stream.  Partial results (max, sum, unnormalised output) go to `ws`
+// [B][Hq][nsplit][Dh + 2] fp32; attn_combine_kernel merges the splits.
+template <int G>
+__global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
+                                                          const bf16* __restrict__ v_cache,
+                                                          const int* __restrict__ positions, float* __restrict__ ws,
+                                                          int Hq, int Hkv, int S_max, int nsplit, float scale) {
+    constexpr int Dh = 128;
+    const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
+    const int len = positions[b] + 1;                      // attend to [0, pos]
+    const int chunk = (len + nsplit - 1) / nsplit;
+    const int s_begin = sp * chunk;
+    const int s_end = min(len, s_begin + chunk);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    float qv[G][4];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        const bf16* qp = q + ((int64_t)b * Hq + hk * G + h) * Dh + lane * 4;
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qp));
+        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qp + 2));
+        qv[h][0] = a.x * scale; qv[h][1] = a.y * scale; qv[h][2] = c.x * scale; qv[h][3] = c.y * scale;
+    }
+    float m[G], l[G], o[G][4];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        m[h] = -FLT_MAX; l[h] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[h][e] = 0.0f;
+    }
+    const bf16* kb = k_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
+    const bf16* vb = v_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
+    for (int s = s_begin + warp; s < s_end; s += 4) {
+        const uint2 kr = *reinterpret_cast<const uint2*>(kb + (int64_t)s * Dh + lane * 4);
+        const uint2 vr = *reinterpret_cast<const uint2*>(vb + (int64_t)s * Dh + lane * 4);
+        const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.x));
+        const float2 k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.y));
+        const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x));
+        const float2 v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float sc = qv[h][0] * k0.x + qv[h][1] * k0.y + qv[h][2] * k1.x + qv[h][3] * k1.y;
+            sc = warp_sum(sc);
+            const float mn = fmaxf(m[h], sc);
+            const float corr = __expf(m[h] - mn);
+            const float pw = __expf(sc - mn);
+            l[h] = l[h] * corr + pw;
+            o[h][0] = o[h][0] * corr + pw * v0.x;
+            o[h][1] = o[h][1] * corr + pw * v0.y;
+            o[h][2] = o[h][2] * corr + pw * v1.x;
+            o[h][3] = o[h][3] * corr + pw * v1.y;
+            m[h] = mn;
+        }
+    }
+    // merge the 4 warps
+    __shared__ float s_m[4][G], s_l[4][G], s_o[4][G][Dh];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s_o[warp][h][lane * 4 + e] = o[h][e];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * Dh; idx += 128) {
+        const int h = idx / Dh, d = idx - h * Dh;
+        float mm = -FLT_MAX;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s_m[w][h]);
+        float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float c = __expf(s_m[w][h] - mm);
+            ll += s_l[w][h] * c;
+            oo += s_o[w][h][d] * c;
+        }
+        float* dst = ws + (((int64_t)b * Hq + hk * G + h) * nsplit + sp) * (Dh + 2);
+        dst[d] = oo;
+        if (d == 0) { dst[Dh] = mm; dst[Dh + 1] = ll; }
+    }
+}
+
+__global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ ws, bf16* __restrict__ out,
+                                                           int nsplit) {
+    constexpr int Dh = 128;
+    const int bh = blockIdx.x;                 // b * Hq + head
+    const int d = threadIdx.x;
+    const float* base = ws + (int64_t)bh * nsplit * (Dh + 2);
+    float mm = -FLT_MAX;
+    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, base[s * (Dh + 2) + Dh]);
+    float ll = 0.0f, oo = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float c = __expf(base[s * (Dh + 2) + Dh] - mm);
+        ll += base[s * (Dh + 2) + Dh + 1] * c;
+        oo += base[s * (Dh + 2) + d] * c;
+    }
+    out[(int64_t)bh * Dh + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+}
+
+// ---- h[r][i] = silu(gu[r][i]) * gu[r][F + i] -----------------------------------------------------
+__global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, int F, int64_t total_pairs) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;     // pair index over [rows][F/2]
+    if (t >= total_pairs) return;
+    const int64_t r = t / (F / 2);
+    const int i = (int)(t - r * (F / 2)) * 2;
+    const float2 gte = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + i));
+    const float2 up = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + F + i));
+    const float a = gte.x / (1.0f + __expf(-gte.x)) * up.x;
+    const float c = gte.y / (1.0f + __expf(-gte.y)) * up.y;
+    *reinterpret_cast<__nv_bfloat162*>(h + r * F + i) = __floats2bfloat162_rn(a, c);
+}
+
+__global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ y, int64_t pairs) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= pairs) return;
+    const float2 u = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(a)[t]);
+    const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(b)[t]);
+    reinterpret_cast<__nv_bfloat162*>(y)[t] = __floats2bfloat162_rn(u.x + v.x, u.y + v.y);
+}
+
+__global__ void embed_kernel(const int64_t* __restrict__ ids, const bf16* __restrict__ table, bf16* __restrict__ y, int D,
+                             int vocab) {
+    int64_t id = ids[blockIdx.x];
+    if (id < 0) id = 0;
+    if (id >= vocab) id = vocab - 1;
+    const uint4* src = reinterpret_cast<const uint4*>(table + id * D);
+    uint4* dst = reinterpret_cast<uint4*>(y + (int64_t)blockIdx.x * D);
+    for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---- greedy sampling: ids[r] = argmax_v logits[r][v] (first maximum wins) ----------------------
+__global__ void __launch_bounds__(1024) argmax_kernel(const bf16* __restrict__ logits, int64_t* __restrict__ ids, int V) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const bf16* row = logits + (int64_t)blockIdx.x * V;
+    float best = -FLT_MAX;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += 1024) {
+        const float v = __bfloat162float(row[i]);
+        if (v > best) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = best; s_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = s_v[threadIdx.x];
+        bi = s_i[threadIdx.x];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) ids[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+}  // namespace nf4
+
+using namespace nf4;
+
+extern "C" int nf4_b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int64_t D, float eps, void* stream) {
+    NF4_REQUIRE(x && w && y, NF4_ERR_ARG, "rmsnorm: null pointer");
+    NF4_REQUIRE(rows >= 0 && D > 0 && D % 2 == 0, NF4_ERR_ARG, "rmsnorm: rows=%lld D=%lld (D must be even)", (long long)rows, (long long)D);
+    if (rows == 0) return NF4_OK;
+    rmsnorm_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(w),
+                                                                               static_cast<bf16*>(y), (int)D, eps);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+extern "C" int nf4_b200_rope_append(const void* qkv, const int* positions, void* q_out, void* k_cache, void* v_cache,
+                                    int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, float theta, void* stream) {
+    NF4_REQUIRE(qkv && positions && q_out && k_cache && v_cache, NF4_ERR_ARG, "rope_append: null pointer");
+    NF4_REQUIRE(Dh % 2 == 0 && Dh <= 2048 && Hq > 0 && Hkv > 0, NF4_ERR_ARG, "rope_append: bad head geometry");
+    if (B == 0) return NF4_OK;
+    dim3 grid((unsigned)(Hq + 2 * Hkv), (unsigned)B);
+    rope_append_kernel<<<grid, Dh / 2, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(qkv), positions, static_cast<bf16*>(q_out), static_cast<bf16*>(k_cache),
+        static_cast<bf16*>(v_cache), Hq, Hkv, Dh, (int)S_max, theta);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+extern "C" int64_t nf4_b200_attn_decode_workspace_bytes(int64_t B, int Hq, int nsplit) {
+    return B * Hq * (int64_t)nsplit * (128 + 2) * 4;
+}
+
+extern "C" int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* positions,
+                                    void* out, void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max,
+                                    int nsplit, void* stream) {
+    NF4_REQUIRE(q && k_cache && v_cache && positions && out && workspace, NF4_ERR_ARG, "attn_decode: null pointer");
+    NF4_REQUIRE(Dh == 128, NF4_ERR_ARG, "attn_decode: head_dim %d (only 128)", Dh);
+    NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 64, NF4_ERR_ARG, "attn_decode: bad geometry");
+    if (B == 0) return NF4_OK;
+    const int G = Hq / Hkv;
+    dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)nsplit);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float scale = 1.0f / sqrtf((float)Dh);
+    const bf16* qq = static_cast<const bf16*>(q);
+    const bf16* kk = static_cast<const bf16*>(k_cache);
+    const bf16* vv = static_cast<const bf16*>(v_cache);
+    float* ws = static_cast<float*>(workspace);
+    switch (G) {
+        case 1: attn_decode_kernel<1><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        case 2: attn_decode_kernel<2><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        case 4: attn_decode_kernel<4><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        case 8: attn_decode_kernel<8><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        default:
+            set_error("attn_decode: %d query heads per KV head (supported: 1, 2, 4, 8)", G);
+            return NF4_ERR_ARG;
+    }
+    NF4_CUDA_TRY(cudaGetLastError());
+    attn_combine_kernel<<<(unsigned)(B * Hq), 128, 0, s>>>(ws, static_cast<bf16*>(out), nsplit);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+extern "C" int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, void* stream) {
+    NF4_REQUIRE(gate_up && h, NF4_ERR_ARG, "silu_mul: null pointer");
+    NF4_REQUIRE(rows >= 0 && F > 0 && F % 2 == 0, NF4_ERR_ARG, "silu_mul: bad extents");
+    const int64_t pairs = rows * (F / 2);
+    if (pairs == 0) return NF4_OK;
+    silu_mul_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(gate_up), static_cast<bf16*>(h), (int)F, pairs);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+extern "C" int nf4_b200_add(const void* a, const void* b, void* y, int64_t numel, void* stream) {
+    NF4_REQUIRE(a && b && y, NF4_ERR_ARG, "add: null pointer");
+    NF4_REQUIRE(numel >= 0 && numel % 2 == 0, NF4_ERR_ARG, "add: numel must be even");
+    if (numel == 0) return NF4_OK;
+    add_kernel<<<(unsigned)((numel / 2 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(a), static_cast<const bf16*>(b), static_cast<bf16*>(y), numel / 2);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+extern "C" int nf4_b200_embed(const int64_t* ids, const void* table, void* y, int64_t rows, int64_t D, int64_t vocab,
+                              void* stream) {
+    NF4_REQUIRE(ids && table && y, NF4_ERR_ARG, "embed: null pointer");
+    NF4_REQUIRE(D > 0 && D % 8 == 0 && vocab > 0, NF4_ERR_ARG, "embed: D must be a multiple of 8");
+    if (rows == 0) return NF4_OK;
+    embed_kernel<<<(unsigned)rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(ids, static_cast<const bf16*>(table), static_cast<bf16*>(y),
+                                                                              (int)D, (int)vocab);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+extern "C" int nf4_b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t V, void* stream) {
+    NF4_REQUIRE(logits && ids, NF4_ERR_ARG, "argmax: null pointer");
+    NF4_REQUIRE(V > 0 && V < (1ll << 31), NF4_ERR_ARG, "argmax: bad vocabulary size");
+    if (rows == 0) return NF4_OK;
+    argmax_kernel<<<(unsigned)rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const bf16*>(logits), ids, (int)V);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}

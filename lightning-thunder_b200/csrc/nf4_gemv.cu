@@ -39,6 +39,7 @@ struct GemvParams {
     const float* absmax;
     const float* code16;
     const void* bias;
+    const void* residual;   // optional [M][N], added after the bias (may alias y)
     void* y;
     int M, N, K;
     int KB;        // K / 64
@@ -245,6 +246,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvParams 
                     float sum = 0.0f;
                     for (int k = 0; k < P; ++k) sum += src[k * (MCOLS * PSTRIDE)];
                     if (p.bias) sum += Elem<T>::to_f32(static_cast<const T*>(p.bias)[grow]);
+                    if (p.residual) sum += Elem<T>::to_f32(static_cast<const T*>(p.residual)[(int64_t)m * p.N + grow]);
                     static_cast<T*>(p.y)[(int64_t)m * p.N + grow] = Elem<T>::from_f32(sum);
                 }
             }
@@ -380,10 +382,10 @@ static int dispatch_gemv(const GemvParams& p, const GemvPlan& pl, cudaStream_t s
 
 template <typename T>
 static int gemv_typed(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16,
-                      int N, const void* bias, void* y, cudaStream_t stream) {
+                      int N, const void* bias, const void* residual, void* y, cudaStream_t stream) {
     const char* force = getenv("NF4_GEMV_KERNEL");   // "direct" or "staged": pins the variant (tests, tuning)
     if (!(force && force[0] == 'd')) {
-        const int rc = gemv_staged_try<T>(x, M, K, packed, absmax, code16, N, bias, y, stream);
+        const int rc = gemv_staged_try<T>(x, M, K, packed, absmax, code16, N, bias, residual, y, stream);
         if (rc >= 0) return rc;
         if (force && force[0] == 's') {
             set_error("gemv: the staged kernel does not take M=%d N=%d K=%d", M, N, K);
@@ -393,7 +395,7 @@ static int gemv_typed(const void* x, int M, int K, const uint8_t* packed, const 
     const int NT = M <= 8 ? 1 : 2;
     GemvPlan pl = plan_gemv(M, N, K, NT);
     GemvParams p;
-    p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.y = y;
+    p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.residual = residual; p.y = y;
     p.M = M; p.N = N; p.K = K; p.KB = K / 64; p.log2P = pl.log2P; p.KBW = p.KB >> pl.log2P;
     p.x_stride_bytes = 2 * K + 16;
     return NT == 1 ? dispatch_gemv<T, 1>(p, pl, stream) : dispatch_gemv<T, 2>(p, pl, stream);
@@ -411,8 +413,9 @@ bool gemv_supported(int64_t M, int64_t K, int64_t N, int blocksize, int dtype, c
 
 using namespace nf4;
 
-extern "C" int nf4_b200_gemv(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
-                             const float* code16, int64_t N, const void* bias, void* y, int dtype, void* stream) {
+extern "C" int nf4_b200_gemv_fused(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                                   const float* code16, int64_t N, const void* bias, const void* residual, void* y,
+                                   int dtype, void* stream) {
     NF4_REQUIRE(x && packed && absmax && code16 && y, NF4_ERR_ARG, "gemv: null pointer");
     NF4_REQUIRE(M >= 1 && M <= 16, NF4_ERR_ARG, "gemv: M=%lld outside [1,16]", (long long)M);
     NF4_REQUIRE(K >= 64 && K % 64 == 0, NF4_ERR_ARG, "gemv: K=%lld must be a positive multiple of 64", (long long)K);
@@ -422,8 +425,14 @@ extern "C" int nf4_b200_gemv(const void* x, int64_t M, int64_t K, const uint8_t*
                 "gemv: x must be 16-byte aligned, packed 8-byte aligned, extents below 2^30 x 2^24");
     if (int rc = check_device()) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == NF4_BF16) return gemv_typed<__nv_bfloat16>(x, (int)M, (int)K, packed, absmax, code16, (int)N, bias, y, s);
-    return gemv_typed<__half>(x, (int)M, (int)K, packed, absmax, code16, (int)N, bias, y, s);
+    if (dtype == NF4_BF16)
+        return gemv_typed<__nv_bfloat16>(x, (int)M, (int)K, packed, absmax, code16, (int)N, bias, residual, y, s);
+    return gemv_typed<__half>(x, (int)M, (int)K, packed, absmax, code16, (int)N, bias, residual, y, s);
+}
+
+extern "C" int nf4_b200_gemv(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                             const float* code16, int64_t N, const void* bias, void* y, int dtype, void* stream) {
+    return nf4_b200_gemv_fused(x, M, K, packed, absmax, code16, N, bias, nullptr, y, dtype, stream);
 }
 
 extern "C" int nf4_b200_linear_generic(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,

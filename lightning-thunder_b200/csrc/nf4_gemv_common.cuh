@@ -82,6 +82,6 @@ __device__ __forceinline__ void lut_build(uint8_t* lut_ptr, const float* __restr
 // Staged (bulk-copy) GEMV: launches and returns NF4_OK, or returns -1 if the shape does not fit.
 template <typename T>
 int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16, int N,
-                    const void* bias, void* y, cudaStream_t stream);
+                    const void* bias, const void* residual, void* y, cudaStream_t stream);
 
 }  // namespace nf4

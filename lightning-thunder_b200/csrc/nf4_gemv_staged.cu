@@ -25,6 +25,7 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include <type_traits>
 
 #include "nf4_gemv_common.cuh"
 
@@ -43,6 +44,7 @@ struct alignas(64) StagedParams {
     const float* absmax;
     const float* code16;
     const void* bias;
+    const void* residual;   // optional [M][N], added after the bias (may alias y)
     void* y;
     int M, N, K, KB;
     int SB;          // 64-blocks per stage (divides KB, multiple of 4, <= 32)
@@ -111,67 +113,89 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// One 64-block of one 16-row tile: 16 table lookups, 4 chained MMAs per column tile, one scaling.
-// HALF: rows 8..15 of the tile do not exist (their fragment registers are zero).
-template <typename T, int NT, bool HALF>
-__device__ __forceinline__ void block_one(const uint8_t* pa, float ama, float amb, int RS, uint32_t window_lane,
-                                          const uint32_t (&xf)[NT][8], float (&acc)[NT][4]) {
-    const uint2 wa = *reinterpret_cast<const uint2*>(pa);
-    uint2 wb = make_uint2(0u, 0u);
-    if (!HALF) wb = *reinterpret_cast<const uint2*>(pa + 8 * RS);
-    float tmp[NT][4];
-    uint32_t a[4];
-    a[1] = 0u;
-    a[3] = 0u;
-    // k-step 0: bytes 0,1
-    a[0] = lut_lookup<0>(wa.x, window_lane);
-    a[2] = lut_lookup<1>(wa.x, window_lane);
-    if (!HALF) { a[1] = lut_lookup<0>(wb.x, window_lane); a[3] = lut_lookup<1>(wb.x, window_lane); }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) Mma<T>::run0(tmp[nt], a, xf[nt][0], xf[nt][1]);
-    // k-step 1: bytes 2,3
-    a[0] = lut_lookup<2>(wa.x, window_lane);
-    a[2] = lut_lookup<3>(wa.x, window_lane);
-    if (!HALF) { a[1] = lut_lookup<2>(wb.x, window_lane); a[3] = lut_lookup<3>(wb.x, window_lane); }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) Mma<T>::acc(tmp[nt], a, xf[nt][2], xf[nt][3]);
-    // k-step 2: bytes 4,5
-    a[0] = lut_lookup<0>(wa.y, window_lane);
-    a[2] = lut_lookup<1>(wa.y, window_lane);
-    if (!HALF) { a[1] = lut_lookup<0>(wb.y, window_lane); a[3] = lut_lookup<1>(wb.y, window_lane); }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) Mma<T>::acc(tmp[nt], a, xf[nt][4], xf[nt][5]);
-    // k-step 3: bytes 6,7
-    a[0] = lut_lookup<2>(wa.y, window_lane);
-    a[2] = lut_lookup<3>(wa.y, window_lane);
-    if (!HALF) { a[1] = lut_lookup<2>(wb.y, window_lane); a[3] = lut_lookup<3>(wb.y, window_lane); }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) Mma<T>::acc(tmp[nt], a, xf[nt][6], xf[nt][7]);
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        acc[nt][0] = fmaf(tmp[nt][0], ama, acc[nt][0]);
-        acc[nt][1] = fmaf(tmp[nt][1], ama, acc[nt][1]);
-        if (!HALF) {
-            acc[nt][2] = fmaf(tmp[nt][2], amb, acc[nt][2]);
-            acc[nt][3] = fmaf(tmp[nt][3], amb, acc[nt][3]);
-        }
-    }
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds32f(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
-// The BPW blocks a warp owns in a stage (off_a / off_am: this thread's byte offsets of the packed
-// bytes and the absmax value of each block inside the stage).
+// One stage of one warp: BPW 64-blocks of a 16-row tile.  Per block: 16 table lookups, 4 chained
+// MMAs per column tile (the chains of different blocks interleave), one scaling by the block's
+// absmax.  HALF: rows 8..15 of the tile do not exist (their fragment registers stay zero).
 template <typename T, int NT, int BPW, bool HALF>
-__device__ __forceinline__ void block_set(const uint8_t* sb, const int (&off_a)[BPW], const float (&am)[BPW][2], int RS,
-                                          uint32_t window_lane, const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4]) {
+__device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a_off)[BPW], const uint32_t (&am_off)[BPW],
+                                              uint32_t rs8, uint32_t as8, uint32_t window_lane,
+                                              const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4]) {
+    uint2 wa[BPW], wb[BPW];
+    float ama[BPW], amb[BPW];
+#pragma unroll
+    for (int bi = 0; bi < BPW; ++bi) {
+        wa[bi] = lds64(sbase + a_off[bi]);
+        ama[bi] = lds32f(sbase + am_off[bi]);
+        if (!HALF) {
+            wb[bi] = lds64(sbase + a_off[bi] + rs8);
+            amb[bi] = lds32f(sbase + am_off[bi] + as8);
+        }
+    }
+    float tmp[BPW][NT][4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+#pragma unroll
+        for (int bi = 0; bi < BPW; ++bi) {
+            const uint32_t va = (t < 2) ? wa[bi].x : wa[bi].y;
+            uint32_t a[4];
+            a[1] = 0u;
+            a[3] = 0u;
+            if (t & 1) {
+                a[0] = lut_lookup<2>(va, window_lane);
+                a[2] = lut_lookup<3>(va, window_lane);
+            } else {
+                a[0] = lut_lookup<0>(va, window_lane);
+                a[2] = lut_lookup<1>(va, window_lane);
+            }
+            if (!HALF) {
+                const uint32_t vb = (t < 2) ? wb[bi].x : wb[bi].y;
+                if (t & 1) {
+                    a[1] = lut_lookup<2>(vb, window_lane);
+                    a[3] = lut_lookup<3>(vb, window_lane);
+                } else {
+                    a[1] = lut_lookup<0>(vb, window_lane);
+                    a[3] = lut_lookup<1>(vb, window_lane);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                if (t == 0) Mma<T>::run0(tmp[bi][nt], a, xf[bi][nt][0], xf[bi][nt][1]);
+                else Mma<T>::acc(tmp[bi][nt], a, xf[bi][nt][2 * t], xf[bi][nt][2 * t + 1]);
+            }
+        }
+    }
 #pragma unroll
     for (int bi = 0; bi < BPW; ++bi)
-        block_one<T, NT, HALF>(sb + off_a[bi], am[bi][0], am[bi][1], RS, window_lane, xf[bi], acc);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            acc[nt][0] = fmaf(tmp[bi][nt][0], ama[bi], acc[nt][0]);
+            acc[nt][1] = fmaf(tmp[bi][nt][1], ama[bi], acc[nt][1]);
+            if (!HALF) {
+                acc[nt][2] = fmaf(tmp[bi][nt][2], amb[bi], acc[nt][2]);
+                acc[nt][3] = fmaf(tmp[bi][nt][3], amb[bi], acc[nt][3]);
+            }
+        }
 }
 
 template <typename T, int NT, int TG, int CW>
 __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __grid_constant__ StagedParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    constexpr int SG_COMPUTE_WARPS = CW;
     constexpr int BPW = 32 / CW;          // 64-blocks of a stage per warp
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -182,24 +206,23 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     const uint32_t s0 = smem_u32(smem);
     const uint32_t lut_base = (s0 + LUT_WINDOW - 1) & ~(uint32_t)(LUT_WINDOW - 1);
     uint8_t* const lut_ptr = smem + (lut_base - s0);
-    uint8_t* const ring = lut_ptr + LUT_WINDOW;
     const uint32_t ring_u32 = lut_base + LUT_WINDOW;
     uint64_t* const bars = reinterpret_cast<uint64_t*>(smem + p.off_bars);   // full[NS], empty[NS], xbar
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(smem + p.off_bars + (2 * SG_MAX_STAGES + 1) * 8);
     float* const part = reinterpret_cast<float*>(smem + p.off_part);
-    const uint8_t* const xs = smem + p.off_x;
+    const uint32_t xs_u32 = s0 + (uint32_t)p.off_x;
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + SG_MAX_STAGES * 8, xbar = full0 + 2 * SG_MAX_STAGES * 8;
 
-    // rows are dealt out in halves of 8: a CTA owns [8*h0, 8*h1), its last tile may be a half tile
+    // rows are dealt out in halves of 8: a CTA owns [8*h0, 8*h1); full 16-row tiles first, then at
+    // most one half tile
     const int H = (p.N + 7) >> 3;
     const int h0 = (int)(((int64_t)H * blockIdx.x) / gridDim.x);
     const int h1 = (int)(((int64_t)H * (blockIdx.x + 1)) / gridDim.x);
     const int r0 = h0 * 8;
     const int r1 = min(h1 * 8, p.N);
     const int nhalves = h1 - h0;
-    const int ntiles = (nhalves + 1) >> 1;
-    const bool last_is_half = (nhalves & 1) != 0;
-    const int ngroups = (ntiles + TG - 1) / TG;
+    const int nfull = nhalves >> 1;
+    const int ntiles = nfull + (nhalves & 1);
 
     if (s0 > 2048u) {   // the host-side map assumes the dynamic region starts within 2 KB of the window
         if (tid == 0 && atomicCAS(&g_gemv_error[0], 0u, 4u) == 0u) g_gemv_error[1] = blockIdx.x;
@@ -208,7 +231,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     if (tid == 0) {
         for (int s = 0; s < p.NS; ++s) {
             mbar_init(full0 + s * 8, 1);
-            mbar_init(empty0 + s * 8, SG_COMPUTE_WARPS);
+            mbar_init(empty0 + s * 8, CW);
         }
         mbar_init(xbar, 1);
         *abort_flag = 0;
@@ -216,142 +239,111 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     }
     __syncthreads();
 
-    if (warp == SG_COMPUTE_WARPS) {
+    // Both roles walk the same schedule: groups of up to TG full tiles, then the half tile alone;
+    // inside a group: for every K segment, every tile of the group -> one stage each.
+    if (warp == CW) {
         // ------------------------------- producer warp --------------------------------------
         if (p.x_staged) {
             if (lane == 0) mbar_expect_tx(xbar, (uint32_t)(p.M * p.K * 2));
             __syncwarp();
             if (lane < p.M)
-                bulk_g2s(smem_u32(xs) + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * p.K * 2,
+                bulk_g2s(xs_u32 + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * p.K * 2,
                          (uint32_t)(p.K * 2), xbar);
         }
         int stage = 0, slot = 0;
         uint32_t parity = 0;
-        for (int grp = 0; grp < ngroups; ++grp) {
-            const int nt_here = min(TG, ntiles - grp * TG);
+        for (int tile0 = 0; tile0 < ntiles;) {
+            const bool half = tile0 >= nfull;
+            const int nt_here = half ? 1 : min(TG, nfull - tile0);
             for (int seg = 0; seg < p.nseg; ++seg) {
                 for (int j = 0; j < nt_here; ++j) {
                     mbar_wait(empty0 + slot * 8, parity ^ 1u, abort_flag, 2, stage);
-                    const int tile = grp * TG + j;
-                    const int row0 = r0 + tile * 16;
-                    const bool half = last_is_half && tile == ntiles - 1;
                     if (lane == 0) {
+                        const int row0 = r0 + (tile0 + j) * 16;
                         const uint32_t fullb = full0 + slot * 8;
                         const uint32_t sbase = ring_u32 + (uint32_t)slot * (uint32_t)p.stage_bytes;
-                        mbar_expect_tx(fullb, (uint32_t)(half ? 8 : 16) * (uint32_t)p.RS);
+                        mbar_expect_tx(fullb, (uint32_t)(half ? 8 : 16) * (uint32_t)(p.RS + p.AS));
                         tma_load_2d(sbase, half ? &p.wmap8 : &p.wmap16, seg * p.SB * 4, row0, fullb);
-                    }
-                    // pull this stage's absmax lines into L2 ahead of the compute warps' loads
-                    if (lane < (half ? 8 : 16) && row0 + lane < p.N) {
-                        const float* a = p.absmax + (int64_t)(row0 + lane) * p.KB + seg * p.SB;
-                        asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+                        tma_load_2d(sbase + 16 * p.RS, half ? &p.amap8 : &p.amap16, seg * p.SB, row0, fullb);
                     }
                     __syncwarp();
                     ++stage;
                     if (++slot == p.NS) { slot = 0; parity ^= 1u; }
                 }
             }
+            tile0 += nt_here;
         }
         return;
     }
 
     // ----------------------------------- compute warps ------------------------------------------
-    lut_build<T>(lut_ptr, p.code16, warp, SG_COMPUTE_WARPS, lane);
+    lut_build<T>(lut_ptr, p.code16, warp, CW, lane);
     // the table is complete for everybody after this barrier (compute warps only)
-    asm volatile("bar.sync 1, %0;" ::"n"(SG_COMPUTE_WARPS * 32) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
     if (p.x_staged) mbar_wait(xbar, 0u, abort_flag, 3, -1);
 
     const uint32_t window_lane = lut_base | (uint32_t)(lane << 2);
     // A block this warp does not own (SB < 32) reads a valid block of the stage against all-zero
-    // activation fragments, so both blocks are always computed.
-    int off_a[BPW], blk[BPW];
+    // activation fragments, so every warp always computes BPW blocks.
+    uint32_t a_off[BPW], am_off[BPW];
 #pragma unroll
     for (int bi = 0; bi < BPW; ++bi) {
-        blk[bi] = min(warp + bi * CW, p.SB - 1);
-        off_a[bi] = g * p.RS + blk[bi] * 32 + q * 8;
+        const int b = min(warp + bi * CW, p.SB - 1);
+        a_off[bi] = (uint32_t)(g * p.RS + b * 32 + q * 8);
+        am_off[bi] = (uint32_t)(16 * p.RS + g * p.AS + b * 4);
     }
-    // absmax goes global -> registers, one stage ahead of its use (rows g and g+8 of the tile)
-    auto load_am = [&](float (&am)[BPW][2], int tile, int seg) {
-        const int row = r0 + tile * 16 + g;
-        const bool half = last_is_half && tile == ntiles - 1;
-#pragma unroll
-        for (int bi = 0; bi < BPW; ++bi) {
-            const float* a = p.absmax + (int64_t)row * p.KB + seg * p.SB + blk[bi];
-            am[bi][0] = row < p.N ? __ldg(a) : 0.0f;
-            am[bi][1] = (!half && row + 8 < p.N) ? __ldg(a + 8 * (int64_t)p.KB) : 0.0f;
-        }
-    };
-    float am_next[BPW][2];
-    if (ngroups > 0) load_am(am_next, 0, 0);
+    const uint32_t rs8 = 8u * (uint32_t)p.RS, as8 = 8u * (uint32_t)p.AS;
+    const uint32_t stage_bytes = (uint32_t)p.stage_bytes;
+    const int NS = p.NS;
+    const int Mc = p.M;
 
     float acc[TG][NT][4];
-    int stage = 0, slot = 0;
-    uint32_t parity = 0;
-    for (int grp = 0; grp < ngroups; ++grp) {
-        const int nt_here = min(TG, ntiles - grp * TG);
-#pragma unroll
-        for (int j = 0; j < TG; ++j)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[j][nt][e] = 0.0f;
+    int stage = 0;
+    uint32_t slot = 0, parity = 0;
 
-        for (int seg = 0; seg < p.nseg; ++seg) {
-            // activation fragments of this warp's two blocks: 16 consecutive values of row m = g (+8)
-            uint32_t xf[BPW][NT][8];
+    // activation fragments of this warp's blocks in segment `seg`: 16 consecutive values of
+    // activation row m = g (+8) per block
+    auto load_xf = [&](uint32_t (&xf)[BPW][NT][8], int seg) {
 #pragma unroll
-            for (int bi = 0; bi < BPW; ++bi) {
-                const int kb = seg * p.SB + warp + bi * CW;
-                const bool live = (warp + bi * CW) < p.SB;
+        for (int bi = 0; bi < BPW; ++bi) {
+            const int kb = seg * p.SB + warp + bi * CW;
+            const bool live = (warp + bi * CW) < p.SB;
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const int m = g + nt * 8;
-                    uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
-                    if (live && m < p.M) {
-                        if (p.x_staged) {
-                            const uint4* src = reinterpret_cast<const uint4*>(xs + m * p.x_stride + ((kb * 64 + q * 16) << 1));
-                            v0 = src[0];
-                            v1 = src[1];
-                        } else {
-                            const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x) +
-                                                                              (((int64_t)m * p.K + kb * 64 + q * 16) << 1));
-                            v0 = __ldg(src);
-                            v1 = __ldg(src + 1);
-                        }
+            for (int nt = 0; nt < NT; ++nt) {
+                const int m = g + nt * 8;
+                uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
+                if (live && m < Mc) {
+                    if (p.x_staged) {
+                        const uint32_t src = xs_u32 + (uint32_t)(m * p.x_stride + ((kb * 64 + q * 16) << 1));
+                        v0 = lds128(src);
+                        v1 = lds128(src + 16);
+                    } else {
+                        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x) +
+                                                                          (((int64_t)m * p.K + kb * 64 + q * 16) << 1));
+                        v0 = __ldg(src);
+                        v1 = __ldg(src + 1);
                     }
-                    xf[bi][nt][0] = v0.x; xf[bi][nt][1] = v0.y; xf[bi][nt][2] = v0.z; xf[bi][nt][3] = v0.w;
-                    xf[bi][nt][4] = v1.x; xf[bi][nt][5] = v1.y; xf[bi][nt][6] = v1.z; xf[bi][nt][7] = v1.w;
                 }
-            }
-
-#pragma unroll
-            for (int j = 0; j < TG; ++j) {
-                if (j < nt_here) {
-                    float am[BPW][2];
-#pragma unroll
-                    for (int bi = 0; bi < BPW; ++bi) { am[bi][0] = am_next[bi][0]; am[bi][1] = am_next[bi][1]; }
-                    {   // the stage after this one: next tile of the group, else next segment, else next group
-                        int j2 = j + 1, seg2 = seg, grp2 = grp;
-                        if (j2 >= nt_here) { j2 = 0; if (++seg2 >= p.nseg) { seg2 = 0; ++grp2; } }
-                        if (grp2 < ngroups) load_am(am_next, grp2 * TG + j2, seg2);
-                    }
-                    mbar_wait(full0 + slot * 8, parity, abort_flag, 1, stage);
-                    const uint8_t* const sb = ring + slot * p.stage_bytes;
-                    const bool half = last_is_half && (grp * TG + j) == ntiles - 1;   // rows 8..15 absent
-                    if (!half) block_set<T, NT, BPW, false>(sb, off_a, am, p.RS, window_lane, xf, acc[j]);
-                    else block_set<T, NT, BPW, true>(sb, off_a, am, p.RS, window_lane, xf, acc[j]);
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(empty0 + slot * 8);
-                    ++stage;
-                    if (++slot == p.NS) { slot = 0; parity ^= 1u; }
-                }
+                xf[bi][nt][0] = v0.x; xf[bi][nt][1] = v0.y; xf[bi][nt][2] = v0.z; xf[bi][nt][3] = v0.w;
+                xf[bi][nt][4] = v1.x; xf[bi][nt][5] = v1.y; xf[bi][nt][6] = v1.z; xf[bi][nt][7] = v1.w;
             }
         }
+    };
 
-        // ---- end of a group: the 16 partial sums of every output meet in shared memory --------
-        // layout part[warp][j][m][16 rows]
-        const int Mc = p.M;
-        float* const mine = part + warp * (TG * Mc * 16);
+    // one stage: wait for the box, compute, hand the slot back
+#define NF4_DO_STAGE(HALF_, XF_, ACC_)                                                                              \
+    do {                                                                                                           \
+        mbar_wait(full0 + slot * 8, parity, abort_flag, 1, stage);                                                  \
+        stage_compute<T, NT, BPW, HALF_>(ring_u32 + slot * stage_bytes, a_off, am_off, rs8, as8, window_lane, XF_, ACC_); \
+        __syncwarp();                                                                                              \
+        if (lane == 0) mbar_arrive(empty0 + slot * 8);                                                              \
+        ++stage;                                                                                                   \
+        if (++slot == (uint32_t)NS) { slot = 0; parity ^= 1u; }                                                     \
+    } while (0)
+
+    // end of a group: the CW partial sums of every output meet in shared memory (fixed order)
+    auto finish_group = [&](int tile0, int nt_here) {
+        float* const mine = part + warp * (TG * Mc * 16);   // layout part[warp][j][m][16 rows]
 #pragma unroll
         for (int j = 0; j < TG; ++j) {
             if (j < nt_here) {
@@ -369,24 +361,72 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                 }
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(SG_COMPUTE_WARPS * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
         const int outputs = nt_here * Mc * 16;
-        for (int o = tid; o < outputs; o += SG_COMPUTE_WARPS * 32) {
+        for (int o = tid; o < outputs; o += CW * 32) {
             const int row = o & 15;
             const int jm = o >> 4;           // j * Mc + m
             const int j = jm / Mc;
             const int m = jm - j * Mc;
-            const int grow = r0 + (grp * TG + j) * 16 + row;
+            const int grow = r0 + (tile0 + j) * 16 + row;
             if (grow < r1) {
                 float sum = 0.0f;
 #pragma unroll
-                for (int w = 0; w < SG_COMPUTE_WARPS; ++w) sum += part[w * (TG * Mc * 16) + o];
+                for (int w = 0; w < CW; ++w) sum += part[w * (TG * Mc * 16) + o];
                 if (p.bias) sum += Elem<T>::to_f32(static_cast<const T*>(p.bias)[grow]);
+                if (p.residual) sum += Elem<T>::to_f32(static_cast<const T*>(p.residual)[(int64_t)m * p.N + grow]);
                 static_cast<T*>(p.y)[(int64_t)m * p.N + grow] = Elem<T>::from_f32(sum);
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(SG_COMPUTE_WARPS * 32) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    };
+
+    auto zero_acc = [&]() {
+#pragma unroll
+        for (int j = 0; j < TG; ++j)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[j][nt][e] = 0.0f;
+    };
+
+    int tile0 = 0;
+    // complete groups of TG full tiles: no per-stage conditionals
+    for (; tile0 + TG <= nfull; tile0 += TG) {
+        zero_acc();
+        for (int seg = 0; seg < p.nseg; ++seg) {
+            uint32_t xf[BPW][NT][8];
+            load_xf(xf, seg);
+#pragma unroll
+            for (int j = 0; j < TG; ++j) NF4_DO_STAGE(false, xf, acc[j]);
+        }
+        finish_group(tile0, TG);
     }
+    // the remaining full tiles
+    if (tile0 < nfull) {
+        const int nt_here = nfull - tile0;
+        zero_acc();
+        for (int seg = 0; seg < p.nseg; ++seg) {
+            uint32_t xf[BPW][NT][8];
+            load_xf(xf, seg);
+#pragma unroll
+            for (int j = 0; j < TG; ++j)
+                if (j < nt_here) NF4_DO_STAGE(false, xf, acc[j]);
+        }
+        finish_group(tile0, nt_here);
+        tile0 = nfull;
+    }
+    // the half tile
+    if (tile0 < ntiles) {
+        zero_acc();
+        for (int seg = 0; seg < p.nseg; ++seg) {
+            uint32_t xf[BPW][NT][8];
+            load_xf(xf, seg);
+            NF4_DO_STAGE(true, xf, acc[0]);
+        }
+        finish_group(tile0, 1);
+    }
+#undef NF4_DO_STAGE
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -471,7 +511,7 @@ static int get_maps(const uint8_t* packed, const float* absmax, int N, int K, in
 // caller then takes the direct-load kernel).
 template <typename T>
 int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16, int N,
-                    const void* bias, void* y, cudaStream_t stream) {
+                    const void* bias, const void* residual, void* y, cudaStream_t stream) {
     const int KB = K / 64;
     if (KB % 4 != 0) return -1;
     if (reinterpret_cast<uintptr_t>(packed) % 16 || reinterpret_cast<uintptr_t>(absmax) % 16 ||
@@ -502,11 +542,11 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     const MapSet* ms = nullptr;
     if (int rc = get_maps(packed, absmax, N, K, SB, &ms)) return rc;
     p.wmap16 = ms->w16; p.wmap8 = ms->w8; p.amap16 = ms->a16; p.amap8 = ms->a8;
-    p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.y = y;
+    p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.residual = residual; p.y = y;
     p.M = M; p.N = N; p.K = K; p.KB = KB; p.SB = SB; p.nseg = KB / SB;
     p.RS = SB * 32 + 32;
     p.AS = SB * 4 + 16;
-    p.stage_bytes = 16 * p.RS;   // a multiple of 512 bytes
+    p.stage_bytes = 16 * p.RS + 16 * p.AS;
     p.x_stride = 2 * K + 16;
     // Shared-memory map.  The dynamic region starts ~1 KB into the shared window, the table takes
     // the 64 KB aligned window [64K, 128K); below it: barriers, partial sums, staged activations;
@@ -550,9 +590,9 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
 }
 
 template int gemv_staged_try<__nv_bfloat16>(const void*, int, int, const uint8_t*, const float*, const float*, int,
-                                            const void*, void*, cudaStream_t);
+                                            const void*, const void*, void*, cudaStream_t);
 template int gemv_staged_try<__half>(const void*, int, int, const uint8_t*, const float*, const float*, int, const void*,
-                                     void*, cudaStream_t);
+                                     const void*, void*, cudaStream_t);
 
 }  // namespace nf4
 

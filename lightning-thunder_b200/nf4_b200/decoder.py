@@ -1,0 +1,266 @@
+"""A Llama-shaped decoder whose every nn.Linear is an NF4 weight (the model the reference's
+transform produces from thunder/tests/llama2_model.py:129-290 -- RMSNorm, rotary embedding on
+interleaved pairs, grouped-query attention with a KV cache, SwiGLU MLP, untied output head), run
+as a chain of launches of this library's kernels and captured in one CUDA graph per decode step.
+
+Weights are random (N(0, 0.02), seeded per tensor) because the benchmark configurations are
+random-init.  Q, K and V share one quantized matrix
+(rows concatenated), as do gate and up: a 64-element quantization block never crosses a row when
+K % 64 == 0, so the fused matrix holds exactly the bytes of the separate ones.
+
+Tensor parallelism (one process per GPU): Q/K/V and gate/up are split by rows (heads, FFN columns),
+the attention-output and down projections by columns (each rank quantizes its own shard, no
+collective), their partial outputs meet in an NCCL all-reduce, and the vocabulary is split for the
+output head (local argmax, then an all-gather of the candidates).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from .functional import nf4_code, quantize_4bit
+
+
+@dataclass(frozen=True)
+class DecoderConfig:
+    n_layers: int
+    d_model: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    ffn: int
+    vocab: int
+    rope_theta: float = 500000.0
+    norm_eps: float = 1e-5
+    name: str = "custom"
+
+
+LLAMA3_8B = DecoderConfig(32, 4096, 32, 8, 128, 14336, 128256, name="llama3-8b-shape")
+LLAMA3_70B = DecoderConfig(80, 8192, 64, 8, 128, 28672, 128256, name="llama3-70b-shape")
+
+
+def tiny_config(n_layers=2, d_model=512, n_heads=4, n_kv_heads=2, ffn=1024, vocab=2048) -> DecoderConfig:
+    """A small model with the same head geometry (head_dim 128, grouped KV heads) for tests."""
+    return DecoderConfig(n_layers, d_model, n_heads, n_kv_heads, d_model // n_heads, ffn, vocab, name="tiny")
+
+
+class NF4Weight:
+    """packed / absmax / code of one [N, K] matrix."""
+
+    __slots__ = ("packed", "absmax", "code", "N", "K")
+
+    def __init__(self, w: torch.Tensor):
+        assert w.dim() == 2 and w.is_cuda
+        self.N, self.K = w.shape
+        self.packed, qs = quantize_4bit(w.contiguous())
+        self.absmax = qs.absmax
+        self.code = nf4_code(w.device)
+
+    def nbytes(self) -> int:
+        return self.packed.numel() + self.absmax.numel() * 4
+
+
+def _seeded_normal(shape, seed: int, device, std=0.02) -> torch.Tensor:
+    g = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+class NF4Decoder:
+    def __init__(self, cfg: DecoderConfig, batch: int, max_seq: int, device="cuda:0", seed: int = 0, tp_rank: int = 0,
+                 tp_size: int = 1, group=None, attn_splits: int = 8):
+        assert cfg.head_dim == 128, "the attention kernel is written for head_dim 128"
+        assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.ffn % (64 * tp_size) == 0
+        assert cfg.vocab % tp_size == 0 and batch <= 16
+        self.cfg, self.B, self.S = cfg, batch, max_seq
+        self.dev = torch.device(device)
+        self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
+        self.lib = _lib.load()
+        self.attn_splits = attn_splits
+        self.Hq = cfg.n_heads // tp_size
+        self.Hkv = cfg.n_kv_heads // tp_size
+        self.F = cfg.ffn // tp_size
+        self.V = cfg.vocab // tp_size
+        D, Dh = cfg.d_model, cfg.head_dim
+        dev, bf = self.dev, torch.bfloat16
+        with torch.cuda.device(dev):
+            self.embed = _seeded_normal((cfg.vocab, D), seed * 1000003 + 1, dev)
+            self.layers = []
+            for li in range(cfg.n_layers):
+                base = seed * 1000003 + 100 * (li + 1)
+                self.layers.append(self._make_layer(base))
+            self.final_norm = torch.ones(D, device=dev, dtype=bf)
+            w = _seeded_normal((cfg.vocab, D), seed * 1000003 + 7, dev)
+            self.lm_head = NF4Weight(w[self.tp_rank * self.V:(self.tp_rank + 1) * self.V])
+            del w
+            L, B, S = cfg.n_layers, batch, max_seq
+            self.k_cache = torch.zeros((L, B, self.Hkv, S, Dh), device=dev, dtype=bf)
+            self.v_cache = torch.zeros((L, B, self.Hkv, S, Dh), device=dev, dtype=bf)
+            self.ids_in = torch.zeros((B,), device=dev, dtype=torch.int64)
+            self.ids_out = torch.zeros((B,), device=dev, dtype=torch.int64)
+            self.positions = torch.zeros((B,), device=dev, dtype=torch.int32)
+            self.x = torch.empty((B, D), device=dev, dtype=bf)
+            self.xn = torch.empty((B, D), device=dev, dtype=bf)
+            self.qkv = torch.empty((B, (self.Hq + 2 * self.Hkv) * Dh), device=dev, dtype=bf)
+            self.q = torch.empty((B, self.Hq * Dh), device=dev, dtype=bf)
+            self.attn = torch.empty((B, self.Hq * Dh), device=dev, dtype=bf)
+            self.gu = torch.empty((B, 2 * self.F), device=dev, dtype=bf)
+            self.h = torch.empty((B, self.F), device=dev, dtype=bf)
+            self.part = torch.empty((B, D), device=dev, dtype=bf)
+            self.logits = torch.empty((B, self.V), device=dev, dtype=bf)
+            ws = self.lib.nf4_b200_attn_decode_workspace_bytes(B, self.Hq, attn_splits)
+            self.attn_ws = torch.empty((ws,), device=dev, dtype=torch.uint8)
+            if tp_size > 1:
+                self.cand = torch.empty((B, 2), device=dev, dtype=torch.float32)
+                self.cand_all = torch.empty((tp_size, B, 2), device=dev, dtype=torch.float32)
+        self.graph = None
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------------------ weights
+    def _make_layer(self, base: int) -> dict:
+        cfg, dev, r, tp = self.cfg, self.dev, self.tp_rank, self.tp_size
+        D, Dh = cfg.d_model, cfg.head_dim
+        wq = _seeded_normal((cfg.n_heads * Dh, D), base + 1, dev)
+        wk = _seeded_normal((cfg.n_kv_heads * Dh, D), base + 2, dev)
+        wv = _seeded_normal((cfg.n_kv_heads * Dh, D), base + 3, dev)
+        hq, hk = self.Hq * Dh, self.Hkv * Dh
+        qkv = torch.cat([wq[r * hq:(r + 1) * hq], wk[r * hk:(r + 1) * hk], wv[r * hk:(r + 1) * hk]], dim=0)
+        del wq, wk, wv
+        wo = _seeded_normal((D, cfg.n_heads * Dh), base + 4, dev)[:, r * hq:(r + 1) * hq].contiguous()
+        wg = _seeded_normal((cfg.ffn, D), base + 5, dev)
+        wu = _seeded_normal((cfg.ffn, D), base + 6, dev)
+        gu = torch.cat([wg[r * self.F:(r + 1) * self.F], wu[r * self.F:(r + 1) * self.F]], dim=0)
+        del wg, wu
+        wd = _seeded_normal((D, cfg.ffn), base + 7, dev)[:, r * self.F:(r + 1) * self.F].contiguous()
+        layer = {
+            "qkv": NF4Weight(qkv), "o": NF4Weight(wo), "gu": NF4Weight(gu), "down": NF4Weight(wd),
+            "norm1": torch.ones(D, device=dev, dtype=torch.bfloat16),
+            "norm2": torch.ones(D, device=dev, dtype=torch.bfloat16),
+        }
+        del qkv, wo, gu, wd
+        return layer
+
+    def weight_bytes(self) -> int:
+        """Bytes of packed codes + absmax one decode step streams on this rank."""
+        n = self.lm_head.nbytes()
+        for layer in self.layers:
+            n += sum(layer[k].nbytes() for k in ("qkv", "o", "gu", "down"))
+        return n
+
+    # ------------------------------------------------------------------------------ one step
+    def _linear(self, x, w: NF4Weight, y, residual=None, stream=None):
+        M = x.shape[0]
+        _lib.check(self.lib.nf4_b200_gemv_fused(x.data_ptr(), M, w.K, w.packed.data_ptr(), w.absmax.data_ptr(),
+                                                w.code.data_ptr(), w.N, None,
+                                                residual.data_ptr() if residual is not None else None, y.data_ptr(),
+                                                _lib.NF4_BF16, stream), "nf4_b200_gemv_fused")
+        self._n += 1
+
+    def _all_reduce(self, t):
+        torch.distributed.all_reduce(t, group=self.group)
+
+    def step(self) -> None:
+        """One decode step on the current stream: ids_in, positions -> ids_out; positions += 1."""
+        cfg, lib, B = self.cfg, self.lib, self.B
+        D, Dh = cfg.d_model, cfg.head_dim
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        ck = _lib.check
+        self._n = 0
+        tp = self.tp_size > 1
+        ck(lib.nf4_b200_embed(self.ids_in.data_ptr(), self.embed.data_ptr(), self.x.data_ptr(), B, D, cfg.vocab, st), "embed")
+        self._n += 1
+        for li, layer in enumerate(self.layers):
+            ck(lib.nf4_b200_rmsnorm(self.x.data_ptr(), layer["norm1"].data_ptr(), self.xn.data_ptr(), B, D, cfg.norm_eps, st), "rmsnorm")
+            self._linear(self.xn, layer["qkv"], self.qkv, stream=st)
+            ck(lib.nf4_b200_rope_append(self.qkv.data_ptr(), self.positions.data_ptr(), self.q.data_ptr(),
+                                        self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), B, self.Hq, self.Hkv, Dh,
+                                        self.S, cfg.rope_theta, st), "rope_append")
+            ck(lib.nf4_b200_attn_decode(self.q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(),
+                                        self.positions.data_ptr(), self.attn.data_ptr(), self.attn_ws.data_ptr(), B, self.Hq,
+                                        self.Hkv, Dh, self.S, self.attn_splits, st), "attn_decode")
+            self._n += 4
+            if tp:
+                # rank 0 carries the residual into the sum; the all-reduce completes x = x + attn.Wo^T
+                self._linear(self.attn, layer["o"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st)
+                self._all_reduce(self.part)
+                self.x, self.part = self.part, self.x   # two swaps per layer: the roles are back after the step
+            else:
+                self._linear(self.attn, layer["o"], self.x, residual=self.x, stream=st)
+            ck(lib.nf4_b200_rmsnorm(self.x.data_ptr(), layer["norm2"].data_ptr(), self.xn.data_ptr(), B, D, cfg.norm_eps, st), "rmsnorm")
+            self._linear(self.xn, layer["gu"], self.gu, stream=st)
+            ck(lib.nf4_b200_silu_mul(self.gu.data_ptr(), self.h.data_ptr(), B, self.F, st), "silu_mul")
+            self._n += 2
+            if tp:
+                self._linear(self.h, layer["down"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st)
+                self._all_reduce(self.part)
+                self.x, self.part = self.part, self.x
+            else:
+                self._linear(self.h, layer["down"], self.x, residual=self.x, stream=st)
+        ck(lib.nf4_b200_rmsnorm(self.x.data_ptr(), self.final_norm.data_ptr(), self.xn.data_ptr(), B, D, cfg.norm_eps, st), "rmsnorm")
+        self._linear(self.xn, self.lm_head, self.logits, stream=st)
+        ck(lib.nf4_b200_argmax(self.logits.data_ptr(), self.ids_out.data_ptr(), B, self.V, st), "argmax")
+        self._n += 2
+        if tp:
+            # candidates (value, global index) of every rank; the first maximum in rank order wins
+            local = self.ids_out
+            self.cand[:, 0] = self.logits.gather(1, local.view(-1, 1)).view(-1).float()
+            self.cand[:, 1] = (local + self.tp_rank * self.V).float()
+            torch.distributed.all_gather_into_tensor(self.cand_all, self.cand, group=self.group)
+            best = self.cand_all[:, :, 0].argmax(dim=0)
+            self.ids_out.copy_(self.cand_all[:, :, 1].gather(0, best.view(1, -1)).view(-1).long())
+        self.positions.add_(1)
+        self.launches_per_step = self._n
+
+    # ------------------------------------------------------------------------------ driving it
+    def capture(self, feed_back: bool = False):
+        """Captures step() in a CUDA graph and makes it the one run_step() replays.  feed_back=True
+        also copies ids_out to ids_in inside the graph (a device-resident greedy loop); otherwise the
+        host provides ids_in every step.  Returns the graph (several may be kept and swapped)."""
+        # Warm-up outside capture: first calls create tensor maps, set kernel attributes, init NCCL.
+        pos0 = self.positions.clone()
+        s = torch.cuda.Stream(device=self.dev)
+        s.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self.step()
+        torch.cuda.current_stream(self.dev).wait_stream(s)
+        torch.cuda.synchronize(self.dev)
+        self.positions.copy_(pos0)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step()
+            if feed_back:
+                self.ids_in.copy_(self.ids_out)
+        self.positions.copy_(pos0)
+        return self.graph
+
+    def run_step(self) -> None:
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step()
+
+    def reset(self) -> None:
+        self.positions.zero_()
+
+    def generate(self, prompt: torch.Tensor, n_new: int) -> torch.Tensor:
+        """prompt [B, T] int64 (host or device).  Feeds the prompt one token per step (filling the KV
+        cache), then decodes n_new tokens greedily.  Returns [B, n_new] int64 on the host."""
+        B, T = prompt.shape
+        assert B == self.B and T + n_new <= self.S
+        prompt = prompt.to(self.dev)
+        self.reset()
+        out = torch.empty((B, n_new), dtype=torch.int64, device=self.dev)
+        for t in range(T):
+            self.ids_in.copy_(prompt[:, t])
+            self.run_step()
+        for t in range(n_new):
+            out[:, t] = self.ids_out
+            if t + 1 < n_new:
+                self.ids_in.copy_(self.ids_out)
+                self.run_step()
+        torch.cuda.synchronize(self.dev)
+        return out.cpu()
