@@ -114,6 +114,26 @@ int nf4_b200_rope_append(const void* qkv, const int* positions, void* q_out, voi
 int64_t nf4_b200_attn_decode_workspace_bytes(int64_t B, int Hq, int nsplit);
 int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* positions, void* out,
                          void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit, void* stream);
+/*
+ * nf4_b200_attn_decode for callers that cannot hand over a scratch buffer.  No counterpart in the
+ * reference.  Meant for hosts that own no device allocator of their own: a plugin living inside a
+ * serving process whose memory pool is private to that process, or a latency-critical loop where
+ * cudaMalloc/cudaFree are ruled out once the service is up (they stall the device and can fail
+ * when memory is fragmented).  Inputs and outputs are still the caller's; only the per-split
+ * partial results go to an array built into the library (nf4_b200_attn_decode_static_max_bytes()
+ * = 4,259,840 bytes, enough for B=16, Hq=64, nsplit=8; each GPU that loads the library holds it
+ * until exit).  A shape that needs more is refused with NF4_ERR_LIMIT.  The function performs no
+ * device allocation or free.
+ *   - The first call on a device looks up the array's device address (with that device current)
+ *     and remembers it; make that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps whatever the last call left there.  Nothing has
+ *     to be cleared: each call writes every slot before reading it.  Two calls that are in flight
+ *     on the GPU at the same time (different streams, or different threads) overwrite each
+ *     other's partial results -- serialise them.
+ */
+int nf4_b200_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const int* positions,
+                                void* out, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit, void* stream);
+int64_t nf4_b200_attn_decode_static_max_bytes(void);
 /* h[r,i] = silu(gate_up[r,i]) * gate_up[r,F+i], gate_up [rows, 2F] */
 int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, void* stream);
 /* y = a + b (numel even) */

@@ -268,9 +268,9 @@ extern "C" int64_t nf4_b200_attn_decode_workspace_bytes(int64_t B, int Hq, int n
     return B * Hq * (int64_t)nsplit * (128 + 2) * 4;
 }
 
-extern "C" int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* positions,
-                                    void* out, void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max,
-                                    int nsplit, void* stream) {
+static int attn_decode_launch(const void* q, const void* k_cache, const void* v_cache, const int* positions, void* out,
+                              void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit,
+                              void* stream) {
     NF4_REQUIRE(q && k_cache && v_cache && positions && out && workspace, NF4_ERR_ARG, "attn_decode: null pointer");
     NF4_REQUIRE(Dh == 128, NF4_ERR_ARG, "attn_decode: head_dim %d (only 128)", Dh);
     NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 64, NF4_ERR_ARG, "attn_decode: bad geometry");
@@ -296,6 +296,53 @@ extern "C" int nf4_b200_attn_decode(const void* q, const void* k_cache, const vo
     attn_combine_kernel<<<(unsigned)(B * Hq), 128, 0, s>>>(ws, static_cast<bf16*>(out), nsplit);
     NF4_CUDA_TRY(cudaGetLastError());
     return NF4_OK;
+}
+
+extern "C" int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* positions,
+                                    void* out, void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max,
+                                    int nsplit, void* stream) {
+    return attn_decode_launch(q, k_cache, v_cache, positions, out, workspace, B, Hq, Hkv, Dh, S_max, nsplit, stream);
+}
+
+// ---- attention without a caller-provided workspace ---------------------------------------------
+// Scratch for the per-split partial results lives in this fixed device array instead of a buffer
+// the caller allocates.  It is sized for the largest decode shape this library targets:
+// 16 batch rows x 64 query heads x 8 sequence splits.  Every GPU that loads the library carries
+// these 4,259,840 bytes until the process exits.
+constexpr int64_t ATTN_STATIC_WS_BYTES = 16ll * 64 * 8 * (128 + 2) * 4;
+static __device__ __align__(256) unsigned char g_attn_static_ws[ATTN_STATIC_WS_BYTES];
+
+// In host code `g_attn_static_ws` is only a handle for the runtime, not an address a kernel can
+// use; the device address has to be asked for, once per device, while that device is current.
+static int attn_static_ws_ptr(void** out) {
+    static void* ptrs[64] = {nullptr};
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    NF4_REQUIRE(dev >= 0 && dev < 64, NF4_ERR_LIMIT, "attn_decode_static: device ordinal %d above 63", dev);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        NF4_CUDA_TRY(cudaGetSymbolAddress(&p, g_attn_static_ws));
+        NF4_REQUIRE(p != nullptr, NF4_ERR_CUDA, "attn_decode_static: cudaGetSymbolAddress returned a null address");
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return NF4_OK;
+}
+
+extern "C" int64_t nf4_b200_attn_decode_static_max_bytes(void) { return ATTN_STATIC_WS_BYTES; }
+
+extern "C" int nf4_b200_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const int* positions,
+                                           void* out, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit,
+                                           void* stream) {
+    NF4_REQUIRE(B >= 0 && Hq > 0 && nsplit >= 1, NF4_ERR_ARG, "attn_decode_static: bad extents");
+    const int64_t need = nf4_b200_attn_decode_workspace_bytes(B, Hq, nsplit);
+    NF4_REQUIRE(need <= ATTN_STATIC_WS_BYTES, NF4_ERR_LIMIT,
+                "attn_decode_static: B=%lld x Hq=%d x nsplit=%d needs %lld bytes of scratch, the built-in array holds %lld "
+                "(16 x 64 x 8); use nf4_b200_attn_decode with your own workspace",
+                (long long)B, Hq, nsplit, (long long)need, (long long)ATTN_STATIC_WS_BYTES);
+    void* ws = nullptr;
+    if (int rc = attn_static_ws_ptr(&ws)) return rc;
+    return attn_decode_launch(q, k_cache, v_cache, positions, out, ws, B, Hq, Hkv, Dh, S_max, nsplit, stream);
 }
 
 extern "C" int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, void* stream) {

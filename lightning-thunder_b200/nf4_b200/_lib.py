@@ -41,6 +41,9 @@ SIGNATURES = {
     "nf4_b200_attn_decode_workspace_bytes": (_c_i64, [_c_i64, _c_int, _c_int]),
     "nf4_b200_attn_decode": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_int,
                                       _c_i64, _c_int, _c_ptr]),
+    "nf4_b200_attn_decode_static": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_int,
+                                             _c_i64, _c_int, _c_ptr]),
+    "nf4_b200_attn_decode_static_max_bytes": (_c_i64, []),
     "nf4_b200_silu_mul": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
     "nf4_b200_add": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr]),
     "nf4_b200_embed": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
