@@ -89,6 +89,23 @@ int nf4_b200_linear_generic(const void* x, int64_t M, int64_t K, const uint8_t* 
                             int dtype, void* stream);
 
 /*
+ * Double quantization of absmax: 8-bit indices into a sorted 256-entry table, one fp32 scale per 256
+ * values, one fp32 offset (device scalar).  The reference leaves this as a TODO
+ * (thunder/transforms/quantization.py:84, 120); results are bit-exact with this library's CPU oracle.
+ *   absmax' = fma(code256[absmax_u8[i]], scale2[i / 256], *offset)
+ * nf4_b200_linear_dq expands absmax into `workspace` (nf4_b200_linear_dq_workspace_bytes(N, K) bytes)
+ * and then runs nf4_b200_linear (blocksize 64).
+ */
+int nf4_b200_dq_quantize(const float* absmax, int64_t nblocks, const float* code256, uint8_t* absmax_u8, float* scale2,
+                         float* offset, void* stream);
+int nf4_b200_dq_dequantize(const uint8_t* absmax_u8, const float* scale2, const float* offset, const float* code256,
+                           int64_t nblocks, float* absmax, void* stream);
+int64_t nf4_b200_linear_dq_workspace_bytes(int64_t N, int64_t K);
+int nf4_b200_linear_dq(const void* x, int64_t M, int64_t K, const uint8_t* packed, const uint8_t* absmax_u8,
+                       const float* scale2, const float* offset, const float* code256, const float* code16, int64_t N,
+                       const void* bias, void* y, int dtype, void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
  * nf4_b200_gemv with one more epilogue term: y = x . dequant(W)^T + bias + residual, residual [M,N]
  * of `dtype` (may be NULL, may alias y).  The reference has no fused form; it is what a decode step
  * needs after the attention-output and MLP-down projections (thunder/tests/llama2_model.py:187-190).
@@ -145,8 +162,9 @@ int nf4_b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t V, v
 
 /*
  * Status word of the kernels that wait on in-kernel barriers (the staged GEMV).  Copies 4 words to
- * host memory: [0] first error code (0 = none; 1/2/3 = a bounded wait on a full/empty/activation
- * barrier ran out, 4 = unexpected shared-memory window), [1] block index, [2] pipeline stage,
+ * host memory: [0] first error code (0 = none; GEMV: 1/2/3 = a bounded wait on a full/empty/activation
+ * barrier ran out, 4 = unexpected shared-memory window; GEMM: 5/6/7/8 = a bounded wait on the
+ * full/empty/weights-ready/accumulator barrier ran out), [1] block index, [2] pipeline stage,
  * [3] number of waits that ran out.  SYNCHRONISES the device; for tests and diagnosis only.  No
  * counterpart in the reference.
  */

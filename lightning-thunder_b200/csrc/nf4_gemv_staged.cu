@@ -598,8 +598,15 @@ template int gemv_staged_try<__half>(const void*, int, int, const uint8_t*, cons
 
 using namespace nf4;
 
+namespace nf4 { int gemm_read_error(unsigned int* out4); }
+
 extern "C" int nf4_b200_device_error(unsigned int* host_out4) {
     NF4_REQUIRE(host_out4, NF4_ERR_ARG, "device_error: null pointer");
     NF4_CUDA_TRY(cudaMemcpyFromSymbol(host_out4, g_gemv_error, sizeof(unsigned int) * 4));
+    if (host_out4[0] == 0) {   // no GEMV error: report the GEMM kernel's word
+        unsigned int g[4] = {0, 0, 0, 0};
+        if (int rc = gemm_read_error(g)) return rc;
+        for (int i = 0; i < 4; ++i) host_out4[i] = g[i];
+    }
     return NF4_OK;
 }

@@ -33,6 +33,11 @@ SIGNATURES = {
     "nf4_b200_linear_generic": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr,
                                          _c_ptr, _c_int, _c_ptr]),
     "nf4_b200_device_error": (_c_int, [_c_ptr]),
+    "nf4_b200_dq_quantize": (_c_int, [_c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
+    "nf4_b200_dq_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr]),
+    "nf4_b200_linear_dq_workspace_bytes": (_c_i64, [_c_i64, _c_i64]),
+    "nf4_b200_linear_dq": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr,
+                                    _c_ptr, _c_int, _c_ptr, _c_i64, _c_ptr]),
     "nf4_b200_gemv_fused": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr,
                                      _c_int, _c_ptr]),
     "nf4_b200_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_float, _c_ptr]),

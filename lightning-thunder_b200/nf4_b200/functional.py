@@ -50,7 +50,9 @@ class QuantState:
         self.blocksize = blocksize
         self.quant_type = quant_type
         self.dtype = dtype
-        self.nested = False
+        self.nested = False     # True after compress_absmax: absmax is uint8, see offset / state2
+        self.offset = None
+        self.state2 = None
 
     def to(self, device):
         self.absmax = self.absmax.to(device)
@@ -72,8 +74,6 @@ def quantize_4bit(A: torch.Tensor, absmax=None, out=None, blocksize: int = 64, c
     """Blockwise NF4 quantization of `A` (fp32/fp16/bf16, any shape).  Returns (packed, QuantState)."""
     if quant_type != "nf4":
         raise NotImplementedError(f"quant_type {quant_type!r}: only 'nf4' is implemented")
-    if compress_statistics:
-        raise NotImplementedError("compress_statistics: use nf4_b200.double_quant for nested absmax")
     if quant_storage != torch.uint8:
         raise NotImplementedError("quant_storage: only torch.uint8")
     if A.dtype not in _DTYPE_CODE:
@@ -95,7 +95,61 @@ def quantize_4bit(A: torch.Tensor, absmax=None, out=None, blocksize: int = 64, c
         )
     state = QuantState(absmax=absmax, shape=A.shape, dtype=A.dtype, blocksize=blocksize, code=code.clone(),
                        quant_type=quant_type)
+    if compress_statistics:
+        compress_absmax(state)
     return out, state
+
+
+_code256_cache: dict = {}
+
+
+def dq_code(device) -> torch.Tensor:
+    """The 256-entry table of the double quantization as an fp32 tensor on `device`."""
+    from .codebook import dq_code256
+
+    device = torch.device(device)
+    key = (device.type, device.index)
+    t = _code256_cache.get(key)
+    if t is None:
+        t = torch.tensor(dq_code256(), dtype=torch.float32, device=device)
+        _code256_cache[key] = t
+    return t
+
+
+def compress_absmax(state: QuantState) -> QuantState:
+    """Double quantization in place: state.absmax becomes uint8 indices, state.state2 holds the
+    per-256 fp32 scales and the table, state.offset the mean that was subtracted (a 1-element
+    tensor on the device)."""
+    am = state.absmax
+    _require_cuda(am, "compress_absmax input")
+    n = am.numel()
+    with torch.cuda.device(am.device):
+        u8 = torch.empty((n,), dtype=torch.uint8, device=am.device)
+        scale2 = torch.empty(((n + 255) // 256,), dtype=torch.float32, device=am.device)
+        offset = torch.empty((1,), dtype=torch.float32, device=am.device)
+        code256 = dq_code(am.device)
+        _lib.check(_lib.load().nf4_b200_dq_quantize(am.data_ptr(), n, code256.data_ptr(), u8.data_ptr(), scale2.data_ptr(),
+                                                    offset.data_ptr(), _stream_ptr(am.device)), "nf4_b200_dq_quantize")
+    state.absmax = u8
+    state.offset = offset
+    state.state2 = QuantState(absmax=scale2, shape=(n,), code=code256, blocksize=256, dtype=torch.float32)
+    state.nested = True
+    return state
+
+
+def expand_absmax(state: QuantState, out=None) -> torch.Tensor:
+    """fp32 absmax of a (possibly double-quantized) state."""
+    if not state.nested:
+        return state.absmax
+    u8 = state.absmax
+    n = u8.numel()
+    with torch.cuda.device(u8.device):
+        if out is None:
+            out = torch.empty((n,), dtype=torch.float32, device=u8.device)
+        _lib.check(_lib.load().nf4_b200_dq_dequantize(u8.data_ptr(), state.state2.absmax.data_ptr(), state.offset.data_ptr(),
+                                                      state.state2.code.data_ptr(), n, out.data_ptr(),
+                                                      _stream_ptr(u8.device)), "nf4_b200_dq_dequantize")
+    return out
 
 
 def dequantize_4bit(A: torch.Tensor, quant_state: QuantState = None, absmax=None, out=None, blocksize: int = 64,
@@ -109,12 +163,13 @@ def dequantize_4bit(A: torch.Tensor, quant_state: QuantState = None, absmax=None
     for s in shape:
         n *= int(s)
     dtype = quant_state.dtype
+    absmax_f32 = expand_absmax(quant_state)
     with torch.cuda.device(A.device):
         if out is None:
             out = torch.empty(tuple(shape), dtype=dtype, device=A.device)
         lib = _lib.load()
         _lib.check(
-            lib.nf4_b200_dequantize(A.data_ptr(), quant_state.absmax.data_ptr(), quant_state.code.data_ptr(), n,
+            lib.nf4_b200_dequantize(A.data_ptr(), absmax_f32.data_ptr(), quant_state.code.data_ptr(), n,
                                     quant_state.blocksize, out.data_ptr(), _DTYPE_CODE[dtype], _stream_ptr(A.device)),
             "nf4_b200_dequantize",
         )
@@ -155,4 +210,37 @@ def matmul_4bit(A: torch.Tensor, B: torch.Tensor, quant_state: QuantState, out=N
     (thunder/transforms/quantization.py:39); quant_state.shape = (N, K)."""
     if quant_state is None:
         raise ValueError("matmul_4bit needs a quant_state")
+    if quant_state.nested:
+        return linear_nf4_dq(A, B, bias, quant_state, out=out)
     return linear_nf4(A, B, bias, quant_state.absmax, quant_state.code, quant_state.blocksize, quant_state.shape, out=out)
+
+
+def linear_nf4_dq(x: torch.Tensor, packed: torch.Tensor, bias, state: QuantState, out=None, workspace=None) -> torch.Tensor:
+    """linear_nf4 for a double-quantized state (C entry point nf4_b200_linear_dq): absmax is expanded
+    into `workspace` (fp32, one value per 64 weights) and the regular kernels run on it."""
+    N, K = int(state.shape[0]), int(state.shape[1])
+    if x.shape[-1] != K:
+        raise RuntimeError(f"linear_nf4_dq: x.shape={tuple(x.shape)} does not match weight shape {(N, K)}")
+    if state.blocksize != 64:
+        raise NotImplementedError("linear_nf4_dq: blocksize 64 only")
+    _require_cuda(x, "linear_nf4_dq input")
+    x2 = x.reshape(-1, K)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    if bias is not None and bias.dtype != x.dtype:
+        bias = bias.to(x.dtype)
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        need = lib.nf4_b200_linear_dq_workspace_bytes(N, K)
+        if workspace is None:
+            workspace = torch.empty((need,), dtype=torch.uint8, device=x.device)
+        if out is None:
+            out = torch.empty((*x.shape[:-1], N), dtype=x.dtype, device=x.device)
+        _lib.check(
+            lib.nf4_b200_linear_dq(x2.data_ptr(), x2.shape[0], K, packed.data_ptr(), state.absmax.data_ptr(),
+                                   state.state2.absmax.data_ptr(), state.offset.data_ptr(), state.state2.code.data_ptr(),
+                                   state.code.data_ptr(), N, bias.data_ptr() if bias is not None else None, out.data_ptr(),
+                                   _DTYPE_CODE[x.dtype], workspace.data_ptr(), workspace.numel(), _stream_ptr(x.device)),
+            "nf4_b200_linear_dq",
+        )
+    return out

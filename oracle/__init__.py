@@ -99,19 +99,21 @@ def dequantize(packed: np.ndarray, absmax: np.ndarray, code16: np.ndarray, numel
     return res
 
 
-GEMM_MODE, GEMV_MODE = 0, 1
+REF_DEQUANT_MATMUL_MODE, GEMV_MODE, GEMM_MODE = 0, 1, 2
 
 
 def linear_mode_for(M: int) -> int:
-    """The regime the library takes for M activation rows (fused GEMV up to 16 rows)."""
+    """The regime the library takes for M activation rows (fused GEMV up to 16 rows, tensor-core
+    GEMM above)."""
     return GEMV_MODE if M <= 16 else GEMM_MODE
 
 
 def linear_bf16(x_bits: np.ndarray, packed, absmax, code16, N: int, K: int, blocksize: int = 64, bias_bits=None,
                 mode=None):
     """x_bits: uint16 [M,K] bf16 bit patterns.  Returns uint16 [M,N] bf16 bit patterns.
-    mode: GEMM_MODE (weights rounded to bf16, then matmul), GEMV_MODE (levels rounded to bf16, block
-    sums scaled in fp32); default = the regime the library takes for this M."""
+    mode: REF_DEQUANT_MATMUL_MODE (weight = bf16(level * absmax)), GEMV_MODE (levels rounded to bf16,
+    block sums scaled in fp32), GEMM_MODE (weight = bf16(bf16(level) * absmax)); default = the
+    regime the library takes for this M."""
     x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16).reshape(-1, K)
     M = x_bits.shape[0]
     code16 = np.ascontiguousarray(code16, dtype=np.float32)

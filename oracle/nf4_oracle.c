@@ -147,6 +147,8 @@ void nf4_oracle_dequantize_bf16(const uint8_t* packed, const float* absmax, cons
  *   mode 1 "fused GEMV" (few activation rows): the 16 levels are rounded to bf16, a 64-block
  *          contributes absmax * sum_k(x[k] * level_bf16[idx[k]]) with the inner sum and the
  *          scaling in fp32 -- no per-weight rounding of the product.
+ *   mode 2 "fused GEMM" (many activation rows, tensor-core operands must be bf16): the weight is
+ *          bf16( bf16(level) * absmax ), i.e. the GEMV's weight rounded once more; fp32 sums.
  * Both round once to bf16 at the end.  The two differ by the bf16 rounding noise of the weights
  * (unit roundoff 2^-8 per weight), which at K >= 4096 exceeds atol 1e-2; a kernel is therefore
  * checked against the mode it implements. */
@@ -165,12 +167,13 @@ void nf4_oracle_linear_bf16(const uint16_t* x, int64_t M, int64_t K, const uint8
                 uint8_t byte = packed[i >> 1];
                 int idx = (i & 1) ? (byte & 15) : (byte >> 4);
                 if (mode == 0) wrow[k] = bf16_bits_to_f32(f32_to_bf16_bits(code16[idx] * absmax[i / blocksize]));
+                else if (mode == 2) wrow[k] = bf16_bits_to_f32(f32_to_bf16_bits(code_r[idx] * absmax[i / blocksize]));
                 else wrow[k] = code_r[idx];
             }
             for (int64_t m = 0; m < M; ++m) {
                 const uint16_t* xr = x + m * K;
                 float s;
-                if (mode == 0) {
+                if (mode != 1) {
                     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                     int64_t k = 0;
                     for (; k + 8 <= K; k += 8)

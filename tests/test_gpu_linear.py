@@ -16,9 +16,9 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 1.6e-2, 1e-2
 
 
-# The M > 16 entry point currently runs the fused-GEMV kernel once per slab of 16 activation rows,
-# so its results follow the oracle's GEMV regime.
-GEMM_ORACLE_MODE = oracle.GEMV_MODE
+# M > 16 in bf16 runs the tcgen05 GEMM (weights = the GEMV's weights rounded to bf16); fp16 runs
+# the GEMV kernel once per slab of 16 activation rows.
+GEMM_ORACLE_MODE = oracle.GEMM_MODE
 
 
 def _oracle_linear(x_cpu, packed_np, absmax_np, code, N, K, bias_cpu=None, mode=None, blocksize=64):
@@ -125,12 +125,41 @@ def test_gemv_is_deterministic(nf4_code_np):
         assert torch.equal(nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs), y0)
 
 
-@pytest.mark.parametrize("M", [17, 64, 256])
-@pytest.mark.parametrize("N,K", [(512, 1024), (4096, 4096)])
+@pytest.mark.parametrize("M", [17, 33, 64, 100, 256, 300, 1000])
+@pytest.mark.parametrize("N,K", [(128, 64), (512, 1024), (4096, 4096), (200, 14336), (1000, 192)])
 def test_gemm_shapes(nf4_code_np, M, N, K):
+    """tcgen05 dequant-GEMM: ragged M and N (tiles of 128 weight rows x up to 256 activation rows),
+    K from one block to 224 blocks."""
+    from nf4_b200 import _lib
+
     w = seeded_weight((N, K), N + K)
     x = seeded_act((M, K), M)
     _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9))
+    assert _lib.device_error()[0] == 0
+
+
+def test_gemm_full_prefill_tile_properties(nf4_code_np):
+    """Config-4-sized problem (2048 activation rows, 14336x4096): compared with an fp32 matmul on the
+    GEMM's own weight definition (torch is only the checker), plus linearity."""
+    import nf4_b200
+
+    N, K, M = 14336, 4096, 2048
+    g = torch.Generator(device="cuda").manual_seed(3)
+    w = (torch.randn((N, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    packed, qs = nf4_b200.quantize_4bit(w)
+    x = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
+    y = nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs)
+    idx = torch.stack([packed.view(-1) >> 4, packed.view(-1) & 15], 1).view(-1).long()
+    wd = (qs.code.to(torch.bfloat16).float()[idx].view(-1, 64) * qs.absmax.view(-1, 1)).view(N, K).to(torch.bfloat16)
+    ref = (x[:256].float() @ wd.float().t())
+    torch.testing.assert_close(y[:256].float(), ref, rtol=RTOL, atol=ATOL)
+    ref = (x[-128:].float() @ wd.float().t())
+    torch.testing.assert_close(y[-128:].float(), ref, rtol=RTOL, atol=ATOL)
+
+
+def test_fp16_many_rows_uses_gemv_slabs(nf4_code_np):
+    w = seeded_weight((512, 1024), 77, dtype=torch.float16)
+    _check(seeded_act((40, 1024), 78, dtype=torch.float16), w, nf4_code_np)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])

@@ -118,7 +118,7 @@ def test_config1_golden(nf4_code_np):
     xs = x.float().numpy().astype(np.float64)[:2]
     # regime "dequantize then matmul": float64 matmul on the bf16-rounded dequantised weight
     wd = oracle.bf16_bits_to_f32(deq).reshape(N, K).astype(np.float64)
-    y0 = oracle.linear_bf16(bf16_bits(x[:2]), packed, absmax, nf4_code_np, N, K, 64, mode=oracle.GEMM_MODE)
+    y0 = oracle.linear_bf16(bf16_bits(x[:2]), packed, absmax, nf4_code_np, N, K, 64, mode=oracle.REF_DEQUANT_MATMUL_MODE)
     assert np.allclose(oracle.bf16_bits_to_f32(y0).astype(np.float64), xs @ wd.T, rtol=1.6e-2, atol=1e-3)
     # regime "fused GEMV": levels rounded to bf16, scaled by the fp32 absmax
     lv = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(nf4_code_np)).astype(np.float64)
@@ -126,7 +126,11 @@ def test_config1_golden(nf4_code_np):
     idx = np.stack([pb >> 4, pb & 15], 1).reshape(N, K)
     wg = lv[idx] * np.repeat(absmax.astype(np.float64), 64).reshape(N, K)
     assert np.allclose(oracle.bf16_bits_to_f32(y[:2]).astype(np.float64), xs @ wg.T, rtol=1.6e-2, atol=1e-3)
-    # the two regimes differ only by bf16 rounding noise of the weights (a few 1e-3 at K=4096)
+    # the tensor-core regime: the GEMV's weights rounded to bf16
+    y2 = oracle.linear_bf16(bf16_bits(x[:2]), packed, absmax, nf4_code_np, N, K, 64, mode=oracle.GEMM_MODE)
+    wg2 = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(wg.astype(np.float32))).astype(np.float64)
+    assert np.allclose(oracle.bf16_bits_to_f32(y2).astype(np.float64), xs @ wg2.T, rtol=1.6e-2, atol=1e-3)
+    # the regimes differ only by bf16 rounding noise of the weights (a few 1e-3 at K=4096)
     d = np.abs(oracle.bf16_bits_to_f32(y0).astype(np.float64) - oracle.bf16_bits_to_f32(y[:2]).astype(np.float64))
     assert d.max() < 0.1 and np.sqrt((d ** 2).mean()) < 1e-2
     # quantization error vs the original weight stays within the NF4 step (max gap/2 * absmax)
