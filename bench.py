@@ -166,7 +166,7 @@ def run_kernel(args):
     def launch_all():
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         for p, qs in ws:
-            if args.kernel == "gemv":
+            if args.kernel in ("gemv", "gemm"):
                 rc = lib.nf4_b200_linear(x.data_ptr(), M, K, p.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N, 64,
                                          None, y.data_ptr(), _lib.NF4_BF16, None, 0, st)
             elif args.kernel == "dequantize":
@@ -177,7 +177,7 @@ def run_kernel(args):
                                            qs.absmax.data_ptr(), st)
             _lib.check(rc, args.kernel)
 
-    deq = torch.empty((N, K), device="cuda", dtype=torch.bfloat16) if args.kernel != "gemv" else None
+    deq = torch.empty((N, K), device="cuda", dtype=torch.bfloat16) if args.kernel not in ("gemv", "gemm") else None
     if deq is not None:
         deq.copy_(nf4_b200.dequantize_4bit(*ws[0]))
     for _ in range(max(1, args.warmup)):
@@ -192,18 +192,27 @@ def run_kernel(args):
         torch.cuda.synchronize()
         ts.append(e0.elapsed_time(e1) * 1e3 / nbuf)
     us = statistics.median(ts)
-    if args.kernel == "gemv":
+    if args.kernel in ("gemv", "gemm"):
         alg = wbytes + 2 * M * K + 2 * M * N
     else:
         alg = 2 * N * K + wbytes
     peaks, src = measured_peaks()
-    print(json.dumps({"kernel": args.kernel, "N": N, "K": K, "M": M, "us_per_launch": us, "algorithmic_bytes": alg,
-                      "GBps": alg / us / 1e3, "frac_of_" + src: alg / us / 1e3 / peaks["hbm_gbs"], "buffers": nbuf}))
+    out = {"kernel": args.kernel, "N": N, "K": K, "M": M, "us_per_launch": us, "algorithmic_bytes": alg,
+           "GBps": alg / us / 1e3, "hbm_frac_of_" + src: alg / us / 1e3 / peaks["hbm_gbs"], "buffers": nbuf}
+    if args.kernel == "gemm":
+        tf = 2.0 * M * N * K / us / 1e6
+        out.update({"TFLOPs": tf, "tensor_frac_of_" + src: tf / peaks["bf16_tflops"]})
+    print(json.dumps(out))
 
 
 # --------------------------------------------------------------------------------------------
 # the decode benchmark
 # --------------------------------------------------------------------------------------------
+
+def _log(msg):
+    if os.environ.get("NF4_BENCH_VERBOSE"):
+        print(f"[bench rank {os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
+
 
 def run_decode(args):
     import torch
@@ -236,13 +245,16 @@ def run_decode(args):
     steps, warmup = args.steps, max(3, args.warmup)
     max_seq = prompt_len + warmup + 2 * steps + 8
 
+    _log(f"building {cfg.name} tp{world}")
     t_build = time.perf_counter()
     dec = NF4Decoder(cfg, batch=batch, max_seq=max_seq, device=dev, seed=1, tp_rank=rank, tp_size=world, group=group)
     torch.cuda.synchronize()
     t_build = time.perf_counter() - t_build
 
+    _log(f"built in {t_build:.1f}s; capturing")
     g_host = dec.capture(feed_back=False)
     g_dev = dec.capture(feed_back=True)
+    _log("captured; filling the KV cache")
     launches = dec.launches_per_step
 
     def barrier():
@@ -261,6 +273,7 @@ def run_decode(args):
         dec.run_step()
     torch.cuda.synchronize()
 
+    _log("prompt done; timing")
     # ---- device-resident greedy loop: `value`
     dec.graph = g_dev
     dec.ids_in.copy_(dec.ids_out)
@@ -329,9 +342,18 @@ def run_decode(args):
     achieved = sum(gemv_bytes) / sum(gemv_us) / 1e3       # GB/s over all GEMV launches of a step
     dev_err = _lib.device_error()
 
-    if rank != 0:
+    def finish():
+        # Tearing down NCCL communicators that captured graphs still reference can block at exit:
+        # meet once more, flush, and leave without running destructors.
+        sys.stdout.flush()
+        sys.stderr.flush()
         if world > 1:
-            torch.distributed.destroy_process_group()
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
 
     cpu_tok_s, t_layer, cores = cpu_decode_sample(workload if workload != "tiny" else "llama3-8b", batch, 3)
@@ -359,8 +381,7 @@ def run_decode(args):
         "build_s": t_build, "device_error": list(dev_err),
     }
     print(json.dumps(line))
-    if world > 1:
-        torch.distributed.destroy_process_group()
+    finish()
 
 
 def main():
@@ -371,7 +392,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "llama3-8b", "llama3-70b", "tiny"])
     ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
-    ap.add_argument("--kernel", default=None, choices=[None, "gemv", "quantize", "dequantize"])
+    ap.add_argument("--kernel", default=None, choices=[None, "gemv", "gemm", "quantize", "dequantize"])
     ap.add_argument("--N", type=int, default=14336)
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--M", type=int, default=1)

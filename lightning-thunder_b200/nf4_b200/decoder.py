@@ -230,7 +230,9 @@ class NF4Decoder:
         torch.cuda.synchronize(self.dev)
         self.positions.copy_(pos0)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        # NCCL's watchdog thread polls events while we capture: keep its calls from invalidating it
+        mode = "thread_local" if self.tp_size > 1 else "global"
+        with torch.cuda.graph(self.graph, capture_error_mode=mode):
             self.step()
             if feed_back:
                 self.ids_in.copy_(self.ids_out)
