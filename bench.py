@@ -321,21 +321,11 @@ def run_decode(args):
     # ---- roofline of the dominant kernel (the fused dequant-GEMV): one more decode step, not
     # captured, with an event pair around every GEMV launch on the launching stream
     dec.graph = None
-    ev = []
-    orig_linear = dec._linear
-
-    def timed_linear(x, w, y, residual=None, stream=None):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        orig_linear(x, w, y, residual=residual, stream=stream)
-        b.record()
-        ev.append((a, b, w.nbytes() + 2 * x.shape[0] * (w.K + w.N)))
-
-    dec._linear = timed_linear
+    dec.gemv_events = ev = []
     dec.ids_in.copy_(dec.ids_out)
     dec.step()
     torch.cuda.synchronize()
-    dec._linear = orig_linear
+    dec.gemv_events = None
     gemv_us = [a.elapsed_time(b) * 1e3 for a, b, _ in ev]
     gemv_bytes = [n for _, _, n in ev]
     peaks, src = measured_peaks()

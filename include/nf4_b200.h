@@ -115,6 +115,25 @@ int nf4_b200_gemv_fused(const void* x, int64_t M, int64_t K, const uint8_t* pack
                         void* stream);
 
 /*
+ * The decode-step form of the fused GEMV (bf16): y = prologue(x) . dequant(W)^T + residual, where the
+ * prologue runs on the activations while they sit in shared memory:
+ *   prologue 0: none;  1: x <- x * rsqrt(mean(x^2) + eps) * norm_w (RMSNorm, norm_w [K]);
+ *   2: x is [M, 2K] = [gate | up] and x <- silu(gate) * up (SwiGLU).
+ * epilogue 0: y [M, N];  1: the weight's rows are (gate_i, up_i) pairs (row 2i, row 2i+1) and
+ *   y [M, N/2] = silu(x.gate_i) * (x.up_i), both sums rounded to bf16 first (no residual).
+ * flags bit 0: launch with programmatic stream serialization (the kernel starts streaming weights
+ * while the previous kernel of the stream is finishing and waits for it before touching x, residual
+ * or y; the previous and next kernels must come from this library).  Returns NF4_ERR_LIMIT when the
+ * prologue's activations do not fit in shared memory (caller runs the separate kernels instead).
+ * No counterpart in the reference: it folds the ops between two linears of
+ * thunder/tests/llama2_model.py:142-190 into the second linear.
+ */
+int nf4_b200_gemv_decode_fits(int64_t M, int64_t N, int64_t K, int prologue);   /* 1 if the call below would fit */
+int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                         const float* code16, int64_t N, const void* residual, void* y, int prologue,
+                         const void* norm_w, float eps, int epilogue, int flags, void* stream);
+
+/*
  * Decode-step glue kernels (bf16 tensors, fp32 arithmetic).  In the reference these ops are lowered
  * by Thunder's executors from the model's trace (RMSNorm, rotary embedding, attention, SwiGLU:
  * thunder/tests/llama2_model.py:20-40, 57-126, 142-190); here they are single launches so that one
@@ -131,6 +150,13 @@ int nf4_b200_rope_append(const void* qkv, const int* positions, void* q_out, voi
 int64_t nf4_b200_attn_decode_workspace_bytes(int64_t B, int Hq, int nsplit);
 int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* positions, void* out,
                          void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit, void* stream);
+/* nf4_b200_rope_append + nf4_b200_attn_decode in ONE launch: reads qkv [B, (Hq+2*Hkv)*Dh], rotates q and
+ * the new k at positions[B], appends k, v to the caches and attends over [0, positions[b]].  `counters`:
+ * B*Hkv unsigned ints that must be zero before the first call (the kernel leaves them zero).  flags bit
+ * 0: programmatic dependent launch (see nf4_b200_gemv_decode).  No counterpart in the reference. */
+int nf4_b200_attn_decode_fused(const void* qkv, const int* positions, void* k_cache, void* v_cache, void* out,
+                               void* workspace, unsigned int* counters, int64_t B, int Hq, int Hkv, int Dh,
+                               int64_t S_max, int nsplit, float theta, int flags, void* stream);
 /*
  * nf4_b200_attn_decode for callers that cannot hand over a scratch buffer.  No counterpart in the
  * reference.  Meant for hosts that own no device allocator of their own: a plugin living inside a
@@ -151,8 +177,9 @@ int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache
 int nf4_b200_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, const int* positions,
                                 void* out, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit, void* stream);
 int64_t nf4_b200_attn_decode_static_max_bytes(void);
-/* h[r,i] = silu(gate_up[r,i]) * gate_up[r,F+i], gate_up [rows, 2F] */
-int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, void* stream);
+/* gate_up [rows, 2F] -> h [rows, F]: interleaved == 0: h[r,i] = silu(gate_up[r,i]) * gate_up[r,F+i];
+ * interleaved != 0: h[r,i] = silu(gate_up[r,2i]) * gate_up[r,2i+1] */
+int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, int interleaved, void* stream);
 /* y = a + b (numel even) */
 int nf4_b200_add(const void* a, const void* b, void* y, int64_t numel, void* stream);
 /* y[r,:] = table[ids[r],:] */

@@ -74,6 +74,48 @@ __global__ void rope_append_kernel(const bf16* __restrict__ qkv, const int* __re
     }
 }
 
+// Merge of the per-split partial results of one (batch row, query head): `base` points at
+// [nsplit][Dh + 2] floats (Dh unnormalised outputs, max, sum).  One warp per head; lane s fetches
+// the (max, sum) of split s, the weights are shared by shuffle and every lane owns 4 output dims,
+// whose nsplit partial vectors are fetched together.  nsplit <= 32.
+__device__ __forceinline__ void merge_splits_warp(const float* __restrict__ base, int nsplit, int lane, bf16* __restrict__ dst) {
+    constexpr int Dh = 128;
+    float mi = -FLT_MAX, li = 0.0f;
+    if (lane < nsplit) {
+        mi = __ldcg(base + lane * (Dh + 2) + Dh);
+        li = __ldcg(base + lane * (Dh + 2) + Dh + 1);
+    }
+    float mm = mi;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    const float ci = lane < nsplit ? __expf(mi - mm) : 0.0f;
+    float ll = li * ci;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, o);
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int s0 = 0; s0 < nsplit; s0 += 8) {
+        float2 lo[8], hi[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int s = s0 + u;
+            lo[u] = make_float2(0.0f, 0.0f);
+            hi[u] = make_float2(0.0f, 0.0f);
+            if (s < nsplit) {   // rows are (Dh+2) floats apart: 8-byte aligned, not 16
+                lo[u] = __ldcg(reinterpret_cast<const float2*>(base + s * (Dh + 2) + lane * 4));
+                hi[u] = __ldcg(reinterpret_cast<const float2*>(base + s * (Dh + 2) + lane * 4 + 2));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float c = __shfl_sync(0xffffffffu, ci, (s0 + u) & 31);
+            acc[0] += lo[u].x * c; acc[1] += lo[u].y * c; acc[2] += hi[u].x * c; acc[3] += hi[u].y * c;
+        }
+    }
+    const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;
+    *reinterpret_cast<__nv_bfloat162*>(dst + lane * 4) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+    *reinterpret_cast<__nv_bfloat162*>(dst + lane * 4 + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+}
+
 // ---- single-query attention over the cache, split along the sequence --------------------------
 // One CTA per (kv head, batch row, split).  Dh = 128: a lane owns 4 dims.  G = Hq/Hkv query heads
 // share the K/V stream.  Partial results (max, sum, unnormalised output) go to `ws`
@@ -158,30 +200,190 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
 }
 
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ ws, bf16* __restrict__ out,
-                                                           int nsplit) {
+                                                           int nsplit, int nheads_total) {
     constexpr int Dh = 128;
-    const int bh = blockIdx.x;                 // b * Hq + head
-    const int d = threadIdx.x;
-    const float* base = ws + (int64_t)bh * nsplit * (Dh + 2);
-    float mm = -FLT_MAX;
-    for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, base[s * (Dh + 2) + Dh]);
-    float ll = 0.0f, oo = 0.0f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float c = __expf(base[s * (Dh + 2) + Dh] - mm);
-        ll += base[s * (Dh + 2) + Dh + 1] * c;
-        oo += base[s * (Dh + 2) + d] * c;
+    const int bh = blockIdx.x * 4 + (threadIdx.x >> 5);       // b * Hq + head, one warp each
+    if (bh >= nheads_total) return;
+    merge_splits_warp(ws + (int64_t)bh * nsplit * (Dh + 2), nsplit, threadIdx.x & 31, out + (int64_t)bh * Dh);
+}
+
+// ---- rotary embedding + KV append + split attention + merge of the splits, one launch ----------
+// Same arithmetic as rope_append_kernel + attn_decode_kernel + attn_combine_kernel (values are
+// rounded to bf16 at the same points), one CTA per (kv head, batch row, split).  The split that
+// owns the current position rotates the new key, writes key and value to the cache and uses them
+// from registers; the last CTA of a (batch row, kv head) to finish -- found with a counter that the
+// kernel leaves at zero again -- merges the partial results.
+template <int G>
+__global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                                         bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                                         bf16* __restrict__ out, float* __restrict__ ws,
+                                                         unsigned int* __restrict__ counters, int Hq, int Hkv, int S_max,
+                                                         int nsplit, float scale, float theta) {
+    constexpr int Dh = 128;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
+    const int pos = positions[b];
+    const int len = pos + 1;
+    const int chunk = (len + nsplit - 1) / nsplit;
+    const int s_begin = sp * chunk;
+    const int s_end = min(len, s_begin + chunk);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bf16* row = qkv + (int64_t)b * (Hq + 2 * Hkv) * Dh;
+
+    // rotation of this lane's two pairs (dims 4*lane .. 4*lane+3)
+    float cs[2], sn[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const float inv_freq = powf(theta, -2.0f * (float)(2 * lane + j) / (float)Dh);
+        sincosf((float)pos * inv_freq, &sn[j], &cs[j]);
     }
-    out[(int64_t)bh * Dh + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+    auto rotate = [&](const bf16* src, float (&r)[4]) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + lane * 4));
+        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + lane * 4 + 2));
+        const float2 ra = __bfloat1622float2(__floats2bfloat162_rn(a.x * cs[0] - a.y * sn[0], a.x * sn[0] + a.y * cs[0]));
+        const float2 rc = __bfloat1622float2(__floats2bfloat162_rn(c.x * cs[1] - c.y * sn[1], c.x * sn[1] + c.y * cs[1]));
+        r[0] = ra.x; r[1] = ra.y; r[2] = rc.x; r[3] = rc.y;
+    };
+    float qv[G][4];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        rotate(row + (hk * G + h) * Dh, qv[h]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qv[h][e] *= scale;
+    }
+    const bool owner = pos >= s_begin && pos < s_end;
+    float knew[4] = {0, 0, 0, 0}, vnew[4] = {0, 0, 0, 0};
+    bf16* kb = k_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
+    bf16* vb = v_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
+    if (owner) {
+        rotate(row + (Hq + hk) * Dh, knew);
+        const bf16* vsrc = row + (Hq + Hkv + hk) * Dh + lane * 4;
+        const uint2 vr = *reinterpret_cast<const uint2*>(vsrc);
+        const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x));
+        const float2 v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
+        vnew[0] = v0.x; vnew[1] = v0.y; vnew[2] = v1.x; vnew[3] = v1.y;
+        if (warp == 0) {
+            *reinterpret_cast<__nv_bfloat162*>(kb + (int64_t)pos * Dh + lane * 4) = __floats2bfloat162_rn(knew[0], knew[1]);
+            *reinterpret_cast<__nv_bfloat162*>(kb + (int64_t)pos * Dh + lane * 4 + 2) = __floats2bfloat162_rn(knew[2], knew[3]);
+            *reinterpret_cast<uint2*>(vb + (int64_t)pos * Dh + lane * 4) = vr;
+        }
+    }
+    float m[G], l[G], o[G][4];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        m[h] = -FLT_MAX; l[h] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[h][e] = 0.0f;
+    }
+    // positions of this warp: s_begin + warp, +4, ...; U of them are fetched before any is used so
+    // the cache reads of a batch overlap (the loop is latency bound otherwise)
+    constexpr int U = 8;
+    for (int s0 = s_begin + warp; s0 < s_end; s0 += 4 * U) {
+        uint2 kr[U], vr[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + 4 * u;
+            kr[u] = make_uint2(0u, 0u);
+            vr[u] = make_uint2(0u, 0u);
+            if (s < s_end && s != pos) {
+                kr[u] = __ldcg(reinterpret_cast<const uint2*>(kb + (int64_t)s * Dh + lane * 4));
+                vr[u] = __ldcg(reinterpret_cast<const uint2*>(vb + (int64_t)s * Dh + lane * 4));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + 4 * u;
+            if (s >= s_end) break;
+            float kf[4], vf[4];
+            if (s == pos) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { kf[e] = knew[e]; vf[e] = vnew[e]; }
+            } else {
+                const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[u].x));
+                const float2 k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[u].y));
+                const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr[u].x));
+                const float2 v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr[u].y));
+                kf[0] = k0.x; kf[1] = k0.y; kf[2] = k1.x; kf[3] = k1.y;
+                vf[0] = v0.x; vf[1] = v0.y; vf[2] = v1.x; vf[3] = v1.y;
+            }
+            float sc[G];
+#pragma unroll
+            for (int h = 0; h < G; ++h) sc[h] = qv[h][0] * kf[0] + qv[h][1] * kf[1] + qv[h][2] * kf[2] + qv[h][3] * kf[3];
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1)
+#pragma unroll
+                for (int h = 0; h < G; ++h) sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], o2);
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                const float mn = fmaxf(m[h], sc[h]);
+                const float corr = __expf(m[h] - mn);
+                const float pw = __expf(sc[h] - mn);
+                l[h] = l[h] * corr + pw;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[h][e] = o[h][e] * corr + pw * vf[e];
+                m[h] = mn;
+            }
+        }
+    }
+    __shared__ float s_m[4][G], s_l[4][G], s_o[4][G][Dh];
+    __shared__ int s_last;
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s_o[warp][h][lane * 4 + e] = o[h][e];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * Dh; idx += 128) {
+        const int h = idx / Dh, d = idx - h * Dh;
+        float mm = -FLT_MAX;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s_m[w][h]);
+        float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float c = __expf(s_m[w][h] - mm);
+            ll += s_l[w][h] * c;
+            oo += s_o[w][h][d] * c;
+        }
+        float* dst = ws + (((int64_t)b * Hq + hk * G + h) * nsplit + sp) * (Dh + 2);
+        dst[d] = oo;
+        if (d == 0) { dst[Dh] = mm; dst[Dh + 1] = ll; }
+    }
+    // ---- the last split to arrive merges ---------------------------------------------------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int old = atomicAdd(&counters[b * Hkv + hk], 1u);
+        s_last = (old == (unsigned int)(nsplit - 1)) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int h = warp; h < G; h += 4) {
+        const int64_t bh = (int64_t)b * Hq + hk * G + h;
+        merge_splits_warp(ws + bh * nsplit * (Dh + 2), nsplit, lane, out + bh * Dh);
+    }
+    if (threadIdx.x == 0) counters[b * Hkv + hk] = 0u;
 }
 
 // ---- h[r][i] = silu(gu[r][i]) * gu[r][F + i] -----------------------------------------------------
-__global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, int F, int64_t total_pairs) {
+__global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, int F, int64_t total_pairs, int interleaved) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;     // pair index over [rows][F/2]
     if (t >= total_pairs) return;
     const int64_t r = t / (F / 2);
     const int i = (int)(t - r * (F / 2)) * 2;
-    const float2 gte = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + i));
-    const float2 up = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + F + i));
+    float2 gte, up;
+    if (interleaved) {   // (gate_i, up_i, gate_i+1, up_i+1) are adjacent
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + 2 * i));
+        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + 2 * i + 2));
+        gte = make_float2(a.x, c.x);
+        up = make_float2(a.y, c.y);
+    } else {
+        gte = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + i));
+        up = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * F + F + i));
+    }
     const float a = gte.x / (1.0f + __expf(-gte.x)) * up.x;
     const float c = gte.y / (1.0f + __expf(-gte.y)) * up.y;
     *reinterpret_cast<__nv_bfloat162*>(h + r * F + i) = __floats2bfloat162_rn(a, c);
@@ -273,7 +475,7 @@ static int attn_decode_launch(const void* q, const void* k_cache, const void* v_
                               void* stream) {
     NF4_REQUIRE(q && k_cache && v_cache && positions && out && workspace, NF4_ERR_ARG, "attn_decode: null pointer");
     NF4_REQUIRE(Dh == 128, NF4_ERR_ARG, "attn_decode: head_dim %d (only 128)", Dh);
-    NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 64, NF4_ERR_ARG, "attn_decode: bad geometry");
+    NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 32, NF4_ERR_ARG, "attn_decode: bad geometry (1 <= nsplit <= 32)");
     if (B == 0) return NF4_OK;
     const int G = Hq / Hkv;
     dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)nsplit);
@@ -293,7 +495,7 @@ static int attn_decode_launch(const void* q, const void* k_cache, const void* v_
             return NF4_ERR_ARG;
     }
     NF4_CUDA_TRY(cudaGetLastError());
-    attn_combine_kernel<<<(unsigned)(B * Hq), 128, 0, s>>>(ws, static_cast<bf16*>(out), nsplit);
+    attn_combine_kernel<<<(unsigned)((B * Hq + 3) / 4), 128, 0, s>>>(ws, static_cast<bf16*>(out), nsplit, (int)(B * Hq));
     NF4_CUDA_TRY(cudaGetLastError());
     return NF4_OK;
 }
@@ -345,13 +547,48 @@ extern "C" int nf4_b200_attn_decode_static(const void* q, const void* k_cache, c
     return attn_decode_launch(q, k_cache, v_cache, positions, out, ws, B, Hq, Hkv, Dh, S_max, nsplit, stream);
 }
 
-extern "C" int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, void* stream) {
+extern "C" int nf4_b200_attn_decode_fused(const void* qkv, const int* positions, void* k_cache, void* v_cache, void* out,
+                                          void* workspace, unsigned int* counters, int64_t B, int Hq, int Hkv, int Dh,
+                                          int64_t S_max, int nsplit, float theta, int flags, void* stream) {
+    NF4_REQUIRE(qkv && positions && k_cache && v_cache && out && workspace && counters, NF4_ERR_ARG, "attn_decode_fused: null pointer");
+    NF4_REQUIRE(Dh == 128, NF4_ERR_ARG, "attn_decode_fused: head_dim %d (only 128)", Dh);
+    NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 32, NF4_ERR_ARG, "attn_decode_fused: bad geometry (1 <= nsplit <= 32)");
+    if (B == 0) return NF4_OK;
+    const int G = Hq / Hkv;
+    NF4_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, NF4_ERR_ARG, "attn_decode_fused: %d query heads per KV head", G);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)Hkv, (unsigned)B, (unsigned)nsplit);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (flags & 1) ? 1 : 0;
+    const float scale = 1.0f / sqrtf((float)Dh);
+    const bf16* a0 = static_cast<const bf16*>(qkv);
+    bf16* a2 = static_cast<bf16*>(k_cache);
+    bf16* a3 = static_cast<bf16*>(v_cache);
+    bf16* a4 = static_cast<bf16*>(out);
+    float* a5 = static_cast<float*>(workspace);
+    const int smax = (int)S_max;
+    switch (G) {
+        case 1: NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_fused_kernel<1>, a0, positions, a2, a3, a4, a5, counters, Hq, Hkv, smax, nsplit, scale, theta)); break;
+        case 2: NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_fused_kernel<2>, a0, positions, a2, a3, a4, a5, counters, Hq, Hkv, smax, nsplit, scale, theta)); break;
+        case 4: NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_fused_kernel<4>, a0, positions, a2, a3, a4, a5, counters, Hq, Hkv, smax, nsplit, scale, theta)); break;
+        default: NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, attn_fused_kernel<8>, a0, positions, a2, a3, a4, a5, counters, Hq, Hkv, smax, nsplit, scale, theta)); break;
+    }
+    return NF4_OK;
+}
+
+extern "C" int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int64_t F, int interleaved, void* stream) {
     NF4_REQUIRE(gate_up && h, NF4_ERR_ARG, "silu_mul: null pointer");
     NF4_REQUIRE(rows >= 0 && F > 0 && F % 2 == 0, NF4_ERR_ARG, "silu_mul: bad extents");
     const int64_t pairs = rows * (F / 2);
     if (pairs == 0) return NF4_OK;
     silu_mul_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const bf16*>(gate_up), static_cast<bf16*>(h), (int)F, pairs);
+        static_cast<const bf16*>(gate_up), static_cast<bf16*>(h), (int)F, pairs, interleaved);
     NF4_CUDA_TRY(cudaGetLastError());
     return NF4_OK;
 }

@@ -382,11 +382,16 @@ static int dispatch_gemv(const GemvParams& p, const GemvPlan& pl, cudaStream_t s
 
 template <typename T>
 static int gemv_typed(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16,
-                      int N, const void* bias, const void* residual, void* y, cudaStream_t stream) {
+                      int N, const void* bias, const void* residual, void* y, cudaStream_t stream,
+                      const GemvOptions& opt = GemvOptions()) {
     const char* force = getenv("NF4_GEMV_KERNEL");   // "direct" or "staged": pins the variant (tests, tuning)
-    if (!(force && force[0] == 'd')) {
-        const int rc = gemv_staged_try<T>(x, M, K, packed, absmax, code16, N, bias, residual, y, stream);
+    if (opt.prologue != 0 || opt.epilogue != 0 || !(force && force[0] == 'd')) {
+        const int rc = gemv_staged_try<T>(x, M, K, packed, absmax, code16, N, bias, residual, y, stream, opt);
         if (rc >= 0) return rc;
+        if (opt.prologue != 0 || opt.epilogue != 0) {
+            set_error("gemv: the fused prologue/epilogue needs M*K small enough to stage the activations (M=%d K=%d) and K a multiple of 256", M, K);
+            return NF4_ERR_LIMIT;
+        }
         if (force && force[0] == 's') {
             set_error("gemv: the staged kernel does not take M=%d N=%d K=%d", M, N, K);
             return NF4_ERR_ARG;
@@ -428,6 +433,25 @@ extern "C" int nf4_b200_gemv_fused(const void* x, int64_t M, int64_t K, const ui
     if (dtype == NF4_BF16)
         return gemv_typed<__nv_bfloat16>(x, (int)M, (int)K, packed, absmax, code16, (int)N, bias, residual, y, s);
     return gemv_typed<__half>(x, (int)M, (int)K, packed, absmax, code16, (int)N, bias, residual, y, s);
+}
+
+extern "C" int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
+                                    const float* code16, int64_t N, const void* residual, void* y, int prologue,
+                                    const void* norm_w, float eps, int epilogue, int flags, void* stream) {
+    NF4_REQUIRE(x && packed && absmax && code16 && y, NF4_ERR_ARG, "gemv_decode: null pointer");
+    NF4_REQUIRE(M >= 1 && M <= 16, NF4_ERR_ARG, "gemv_decode: M=%lld outside [1,16]", (long long)M);
+    NF4_REQUIRE(K >= 64 && K % 64 == 0 && N >= 1, NF4_ERR_ARG, "gemv_decode: bad extents N=%lld K=%lld", (long long)N, (long long)K);
+    NF4_REQUIRE(prologue >= 0 && prologue <= 2, NF4_ERR_ARG, "gemv_decode: prologue %d", prologue);
+    NF4_REQUIRE(prologue != 1 || norm_w, NF4_ERR_ARG, "gemv_decode: the rmsnorm prologue needs norm_w");
+    NF4_REQUIRE(epilogue == 0 || (epilogue == 1 && !residual && N % 2 == 0), NF4_ERR_ARG,
+                "gemv_decode: the SwiGLU epilogue takes an even N and no residual");
+    NF4_REQUIRE(gemv_supported(M, K, N, 64, NF4_BF16, x, packed, absmax), NF4_ERR_ALIGN,
+                "gemv_decode: x must be 16-byte aligned, packed 8-byte aligned");
+    if (int rc = check_device()) return rc;
+    GemvOptions opt;
+    opt.prologue = prologue; opt.norm_w = norm_w; opt.eps = eps; opt.epilogue = epilogue; opt.pdl = (flags & 1) != 0;
+    return gemv_typed<__nv_bfloat16>(x, (int)M, (int)K, packed, absmax, code16, (int)N, nullptr, residual, y,
+                                     static_cast<cudaStream_t>(stream), opt);
 }
 
 extern "C" int nf4_b200_gemv(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,

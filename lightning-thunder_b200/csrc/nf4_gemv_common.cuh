@@ -79,9 +79,19 @@ __device__ __forceinline__ void lut_build(uint8_t* lut_ptr, const float* __restr
     }
 }
 
-// Staged (bulk-copy) GEMV: launches and returns NF4_OK, or returns -1 if the shape does not fit.
+struct GemvOptions {
+    int prologue = 0;             // 0 none, 1 rmsnorm(x) * norm_w, 2 silu(x[:, :K]) * x[:, K:]
+    const void* norm_w = nullptr;
+    float eps = 0.0f;
+    int epilogue = 0;             // 0 none, 1 SwiGLU over (gate, up) row pairs (output has N/2 columns)
+    bool pdl = false;             // launch with programmatic stream serialization
+    bool dry_run = false;         // plan only: report whether the shape (and prologue) fits
+};
+
+// Staged (TMA ring) GEMV: launches and returns NF4_OK (or an error code); returns -1 if the shape does
+// not fit the kernel, -2 if only the requested prologue does not fit.
 template <typename T>
 int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16, int N,
-                    const void* bias, const void* residual, void* y, cudaStream_t stream);
+                    const void* bias, const void* residual, void* y, cudaStream_t stream, const GemvOptions& opt);
 
 }  // namespace nf4

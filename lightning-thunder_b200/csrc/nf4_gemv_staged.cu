@@ -54,12 +54,24 @@ struct alignas(64) StagedParams {
     int AS;          // bytes between absmax rows inside a stage (SB*4 + 16)
     int stage_bytes; // 16*RS + 16*AS
     int x_staged;    // activations are copied to shared memory
-    int x_stride;    // bytes between staged activation rows (2K + 16)
+    int x_stride;    // bytes between staged activation rows (2K + 16; 4K + 16 with the SiLU prologue)
+    int prologue;    // 0: none; 1: x <- rmsnorm(x) * norm_w; 2: x <- silu(x[:, :K]) * x[:, K:2K]  (x is [M][2K])
+    const void* norm_w;   // [K], prologue 1
+    float eps;
+    int epilogue;    // 0: y[m][n]; 1: rows come in (gate, up) pairs and y[m][n/2] = silu(gate) * up
     // offsets from the start of dynamic shared memory
     int off_bars, off_part, off_x;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start
+// while its predecessor is still running; `griddep_wait` blocks until the predecessor grid has
+// finished and its writes are visible (no-op for a normal launch), `griddep_launch` lets the
+// successor start early.  Everything before the wait may only touch weights and the kernel's own
+// shared memory.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -238,18 +250,25 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    griddep_launch();
 
     // Both roles walk the same schedule: groups of up to TG full tiles, then the half tile alone;
     // inside a group: for every K segment, every tile of the group -> one stage each.
     if (warp == CW) {
         // ------------------------------- producer warp --------------------------------------
-        if (p.x_staged) {
-            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)(p.M * p.K * 2));
+        // The weights do not depend on the previous kernel: the ring is filled first, the
+        // activations are fetched once the predecessor grid has finished.
+        const uint32_t x_row_bytes = (uint32_t)(p.K * 2) * (p.prologue == 2 ? 2u : 1u);
+        bool x_issued = !p.x_staged;
+        auto issue_x = [&]() {
+            griddep_wait();
+            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)p.M * x_row_bytes);
             __syncwarp();
             if (lane < p.M)
-                bulk_g2s(xs_u32 + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * p.K * 2,
-                         (uint32_t)(p.K * 2), xbar);
-        }
+                bulk_g2s(xs_u32 + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * x_row_bytes,
+                         x_row_bytes, xbar);
+            x_issued = true;
+        };
         int stage = 0, slot = 0;
         uint32_t parity = 0;
         for (int tile0 = 0; tile0 < ntiles;) {
@@ -257,6 +276,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             const int nt_here = half ? 1 : min(TG, nfull - tile0);
             for (int seg = 0; seg < p.nseg; ++seg) {
                 for (int j = 0; j < nt_here; ++j) {
+                    if (!x_issued && stage >= p.NS) issue_x();
                     mbar_wait(empty0 + slot * 8, parity ^ 1u, abort_flag, 2, stage);
                     if (lane == 0) {
                         const int row0 = r0 + (tile0 + j) * 16;
@@ -273,6 +293,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             }
             tile0 += nt_here;
         }
+        if (!x_issued) issue_x();
         return;
     }
 
@@ -280,7 +301,89 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     lut_build<T>(lut_ptr, p.code16, warp, CW, lane);
     // the table is complete for everybody after this barrier (compute warps only)
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    // RMSNorm weights are parameters, not activations: fetch them before waiting for the predecessor
+    constexpr int NTH = CW * 32;
+    constexpr int NWC = 8;                          // pairs per thread held in registers (K <= 16 * NTH)
+    __nv_bfloat162 nw_cache[NWC];
+    const bool nw_cached = p.prologue == 1 && p.K / 2 <= NWC * NTH;
+    if (nw_cached) {
+        const __nv_bfloat162* nw = static_cast<const __nv_bfloat162*>(p.norm_w);
+#pragma unroll
+        for (int j = 0; j < NWC; ++j) {
+            const int i = tid + j * NTH;
+            nw_cache[j] = i < p.K / 2 ? nw[i] : __floats2bfloat162_rn(0.0f, 0.0f);
+        }
+    }
+    griddep_wait();
     if (p.x_staged) mbar_wait(xbar, 0u, abort_flag, 3, -1);
+
+    // ---- optional prologue on the staged activations (in place, every CTA for itself) ----------
+    if (p.prologue != 0) {
+        uint8_t* const xsp = smem + p.off_x;
+        const int ctid = tid;                       // 0 .. CW*32-1
+        if (p.prologue == 1) {
+            float* const red = part;                // 2*CW floats of scratch (free before the first group ends)
+            for (int m = 0; m < p.M; ++m) {
+                __nv_bfloat162* row = reinterpret_cast<__nv_bfloat162*>(xsp + m * p.x_stride);
+                float* const redm = red + (m & 1) * CW;   // alternate so one barrier per row is enough
+                if (nw_cached) {
+                    float2 v[NWC];
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < NWC; ++j) {
+                        const int i = ctid + j * NTH;
+                        v[j] = i < p.K / 2 ? __bfloat1622float2(row[i]) : make_float2(0.0f, 0.0f);
+                        ss += v[j].x * v[j].x + v[j].y * v[j].y;
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (lane == 0) redm[warp] = ss;
+                    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+                    float tot = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < CW; ++w) tot += redm[w];
+                    const float r = rsqrtf(tot / (float)p.K + p.eps);
+#pragma unroll
+                    for (int j = 0; j < NWC; ++j) {
+                        const int i = ctid + j * NTH;
+                        const float2 gw = __bfloat1622float2(nw_cache[j]);
+                        if (i < p.K / 2) row[i] = __floats2bfloat162_rn(v[j].x * r * gw.x, v[j].y * r * gw.y);
+                    }
+                } else {
+                    float ss = 0.0f;
+                    for (int i = ctid; i < p.K / 2; i += NTH) {
+                        const float2 v = __bfloat1622float2(row[i]);
+                        ss += v.x * v.x + v.y * v.y;
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (lane == 0) redm[warp] = ss;
+                    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+                    float tot = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < CW; ++w) tot += redm[w];
+                    const float r = rsqrtf(tot / (float)p.K + p.eps);
+                    const __nv_bfloat162* nw = static_cast<const __nv_bfloat162*>(p.norm_w);
+                    for (int i = ctid; i < p.K / 2; i += NTH) {
+                        const float2 v = __bfloat1622float2(row[i]);
+                        const float2 gw = __bfloat1622float2(nw[i]);
+                        row[i] = __floats2bfloat162_rn(v.x * r * gw.x, v.y * r * gw.y);
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+        } else {
+            for (int m = 0; m < p.M; ++m) {
+                __nv_bfloat162* row = reinterpret_cast<__nv_bfloat162*>(xsp + m * p.x_stride);
+                for (int i = ctid; i < p.K / 2; i += NTH) {
+                    const float2 gt = __bfloat1622float2(row[i]);
+                    const float2 up = __bfloat1622float2(row[i + p.K / 2]);
+                    row[i] = __floats2bfloat162_rn(gt.x / (1.0f + __expf(-gt.x)) * up.x, gt.y / (1.0f + __expf(-gt.y)) * up.y);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+        }
+    }
 
     const uint32_t window_lane = lut_base | (uint32_t)(lane << 2);
     // A block this warp does not own (SB < 32) reads a valid block of the stage against all-zero
@@ -362,6 +465,33 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+        if (p.epilogue == 1) {
+            // SwiGLU: weight rows 2i / 2i+1 are gate_i / up_i; both sums are rounded to the activation
+            // type first (what a separate kernel would read back), then h_i = silu(gate_i) * up_i
+            const int pairs = nt_here * Mc * 8;
+            const int half_n = p.N >> 1;
+            for (int o = tid; o < pairs; o += CW * 32) {
+                const int pr = o & 7;
+                const int jm = o >> 3;
+                const int j = jm / Mc;
+                const int m = jm - j * Mc;
+                const int grow = r0 + (tile0 + j) * 16 + 2 * pr;
+                if (grow < r1) {
+                    float sg = 0.0f, su = 0.0f;
+                    const int idx = jm * 16 + 2 * pr;
+#pragma unroll
+                    for (int w = 0; w < CW; ++w) {
+                        sg += part[w * (TG * Mc * 16) + idx];
+                        su += part[w * (TG * Mc * 16) + idx + 1];
+                    }
+                    const float gt = Elem<T>::to_f32(Elem<T>::from_f32(sg));
+                    const float up = Elem<T>::to_f32(Elem<T>::from_f32(su));
+                    static_cast<T*>(p.y)[(int64_t)m * half_n + (grow >> 1)] = Elem<T>::from_f32(gt / (1.0f + __expf(-gt)) * up);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+            return;
+        }
         const int outputs = nt_here * Mc * 16;
         for (int o = tid; o < outputs; o += CW * 32) {
             const int row = o & 15;
@@ -431,6 +561,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
 
 // ---------------------------------------------------------------------------------------------
 
+static thread_local bool g_launch_pdl = false;   // set by the entry point for the duration of one call
+
 template <typename T, int NT, int TG, int CW>
 static int launch_staged(const StagedParams& p, int grid, cudaStream_t stream) {
     static bool configured[64] = {false};
@@ -440,7 +572,21 @@ static int launch_staged(const StagedParams& p, int grid, cudaStream_t stream) {
         NF4_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<T, NT, TG, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM));
         configured[dev] = true;
     }
-    gemv_staged_kernel<T, NT, TG, CW><<<grid, (CW + 1) * 32, GEMV_SMEM, stream>>>(p);
+    if (g_launch_pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid);
+        cfg.blockDim = dim3((CW + 1) * 32);
+        cfg.dynamicSmemBytes = GEMV_SMEM;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_staged_kernel<T, NT, TG, CW>, p));
+    } else {
+        gemv_staged_kernel<T, NT, TG, CW><<<grid, (CW + 1) * 32, GEMV_SMEM, stream>>>(p);
+    }
     NF4_CUDA_TRY(cudaGetLastError());
     return NF4_OK;
 }
@@ -511,7 +657,7 @@ static int get_maps(const uint8_t* packed, const float* absmax, int N, int K, in
 // caller then takes the direct-load kernel).
 template <typename T>
 int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const float* absmax, const float* code16, int N,
-                    const void* bias, const void* residual, void* y, cudaStream_t stream) {
+                    const void* bias, const void* residual, void* y, cudaStream_t stream, const GemvOptions& opt) {
     const int KB = K / 64;
     if (KB % 4 != 0) return -1;
     if (reinterpret_cast<uintptr_t>(packed) % 16 || reinterpret_cast<uintptr_t>(absmax) % 16 ||
@@ -539,15 +685,14 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     }
 
     StagedParams p;
-    const MapSet* ms = nullptr;
-    if (int rc = get_maps(packed, absmax, N, K, SB, &ms)) return rc;
-    p.wmap16 = ms->w16; p.wmap8 = ms->w8; p.amap16 = ms->a16; p.amap8 = ms->a8;
     p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.residual = residual; p.y = y;
     p.M = M; p.N = N; p.K = K; p.KB = KB; p.SB = SB; p.nseg = KB / SB;
     p.RS = SB * 32 + 32;
     p.AS = SB * 4 + 16;
     p.stage_bytes = 16 * p.RS + 16 * p.AS;
-    p.x_stride = 2 * K + 16;
+    p.prologue = opt.prologue; p.norm_w = opt.norm_w; p.eps = opt.eps; p.epilogue = opt.epilogue;
+    if (opt.epilogue == 1 && (N % 2 != 0)) return -2;
+    p.x_stride = (opt.prologue == 2 ? 4 : 2) * K + 16;
     // Shared-memory map.  The dynamic region starts ~1 KB into the shared window, the table takes
     // the 64 KB aligned window [64K, 128K); below it: barriers, partial sums, staged activations;
     // above it: the ring (every stage and both boxes inside it start on a 128-byte boundary).
@@ -563,6 +708,7 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     p.off_x = (p.off_part + part_bytes + 127) & ~127;
     if (p.off_x > low_cap) return -1;
     p.x_staged = ((int64_t)p.off_x + (int64_t)M * p.x_stride <= low_cap) ? 1 : 0;
+    if (opt.prologue != 0 && !p.x_staged) return -2;   // a prologue needs the activations in shared memory
     const int ring_cap = GEMV_SMEM - 2 * LUT_WINDOW;   // the window ends at most 128 KB into the region
     int NS = ring_cap / p.stage_bytes;
     if (NS > SG_MAX_STAGES) NS = SG_MAX_STAGES;
@@ -572,7 +718,12 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         if (v >= 2 && v <= NS) NS = v;
     }
     p.NS = NS;
+    if (opt.dry_run) return NF4_OK;
+    const MapSet* ms = nullptr;
+    if (int rc = get_maps(packed, absmax, N, K, SB, &ms)) return rc;
+    p.wmap16 = ms->w16; p.wmap8 = ms->w8; p.amap16 = ms->a16; p.amap8 = ms->a8;
 
+    g_launch_pdl = opt.pdl;
 #define NF4_SG(NT_, TG_)                                                        \
     do {                                                                        \
         if (CW == 8) return launch_staged<T, NT_, TG_, 8>(p, grid, stream);     \
@@ -590,15 +741,26 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
 }
 
 template int gemv_staged_try<__nv_bfloat16>(const void*, int, int, const uint8_t*, const float*, const float*, int,
-                                            const void*, const void*, void*, cudaStream_t);
+                                            const void*, const void*, void*, cudaStream_t, const GemvOptions&);
 template int gemv_staged_try<__half>(const void*, int, int, const uint8_t*, const float*, const float*, int, const void*,
-                                     const void*, void*, cudaStream_t);
+                                     const void*, void*, cudaStream_t, const GemvOptions&);
 
 }  // namespace nf4
 
 using namespace nf4;
 
 namespace nf4 { int gemm_read_error(unsigned int* out4); }
+
+extern "C" int nf4_b200_gemv_decode_fits(int64_t M, int64_t N, int64_t K, int prologue) {
+    if (M < 1 || M > 16 || N < 1 || K < 64 || K % 64 != 0 || prologue < 0 || prologue > 2) return 0;
+    GemvOptions opt;
+    opt.prologue = prologue;
+    opt.dry_run = true;
+    const void* aligned = reinterpret_cast<const void*>(uintptr_t(256));
+    return gemv_staged_try<__nv_bfloat16>(aligned, (int)M, (int)K, static_cast<const uint8_t*>(aligned),
+                                          static_cast<const float*>(aligned), nullptr, (int)N, nullptr, nullptr, nullptr,
+                                          nullptr, opt) == NF4_OK ? 1 : 0;
+}
 
 extern "C" int nf4_b200_device_error(unsigned int* host_out4) {
     NF4_REQUIRE(host_out4, NF4_ERR_ARG, "device_error: null pointer");

@@ -40,16 +40,21 @@ SIGNATURES = {
                                     _c_ptr, _c_int, _c_ptr, _c_i64, _c_ptr]),
     "nf4_b200_gemv_fused": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr,
                                      _c_int, _c_ptr]),
+    "nf4_b200_gemv_decode": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int, _c_ptr,
+                                      ctypes.c_float, _c_int, _c_int, _c_ptr]),
+    "nf4_b200_gemv_decode_fits": (_c_int, [_c_i64, _c_i64, _c_i64, _c_int]),
     "nf4_b200_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_float, _c_ptr]),
     "nf4_b200_rope_append": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_int, _c_i64,
                                       ctypes.c_float, _c_ptr]),
     "nf4_b200_attn_decode_workspace_bytes": (_c_i64, [_c_i64, _c_int, _c_int]),
     "nf4_b200_attn_decode": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_int,
                                       _c_i64, _c_int, _c_ptr]),
+    "nf4_b200_attn_decode_fused": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int,
+                                            _c_int, _c_i64, _c_int, ctypes.c_float, _c_int, _c_ptr]),
     "nf4_b200_attn_decode_static": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_int,
                                              _c_i64, _c_int, _c_ptr]),
     "nf4_b200_attn_decode_static_max_bytes": (_c_i64, []),
-    "nf4_b200_silu_mul": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
+    "nf4_b200_silu_mul": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_ptr]),
     "nf4_b200_add": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr]),
     "nf4_b200_embed": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
     "nf4_b200_argmax": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),

@@ -5,8 +5,8 @@ as a chain of launches of this library's kernels and captured in one CUDA graph 
 
 Weights are random (N(0, 0.02), seeded per tensor) because the benchmark configurations are
 random-init.  Q, K and V share one quantized matrix
-(rows concatenated), as do gate and up: a 64-element quantization block never crosses a row when
-K % 64 == 0, so the fused matrix holds exactly the bytes of the separate ones.
+(rows concatenated), as do gate and up (rows interleaved): a 64-element quantization block never
+crosses a row when K % 64 == 0, so the fused matrix holds exactly the bytes of the separate ones.
 
 Tensor parallelism (one process per GPU): Q/K/V and gate/up are split by rows (heads, FFN columns),
 the attention-output and down projections by columns (each rank quantizes its own shard, no
@@ -71,7 +71,7 @@ def _seeded_normal(shape, seed: int, device, std=0.02) -> torch.Tensor:
 
 class NF4Decoder:
     def __init__(self, cfg: DecoderConfig, batch: int, max_seq: int, device="cuda:0", seed: int = 0, tp_rank: int = 0,
-                 tp_size: int = 1, group=None, attn_splits: int = 8):
+                 tp_size: int = 1, group=None, attn_splits: int | None = None, fused: bool = True, pdl: bool = True):
         assert cfg.head_dim == 128, "the attention kernel is written for head_dim 128"
         assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.ffn % (64 * tp_size) == 0
         assert cfg.vocab % tp_size == 0 and batch <= 16
@@ -79,7 +79,15 @@ class NF4Decoder:
         self.dev = torch.device(device)
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
         self.lib = _lib.load()
+        if attn_splits is None:     # enough CTAs (kv heads x rows x splits) to cover the SMs twice
+            attn_splits = max(1, min(16, 296 // max(1, (cfg.n_kv_heads // tp_size) * batch)))
         self.attn_splits = attn_splits
+        # fused: RMSNorm and SiLU*up run as prologues of the following GEMV (where the activations fit
+        # in shared memory), rotary embedding + KV append + attention + merge are one launch.
+        # pdl: those launches use programmatic dependent launch (weight streaming of a kernel overlaps
+        # the tail of its predecessor).
+        self.fused = fused
+        self.flags = 1 if (fused and pdl) else 0
         self.Hq = cfg.n_heads // tp_size
         self.Hkv = cfg.n_kv_heads // tp_size
         self.F = cfg.ffn // tp_size
@@ -113,11 +121,13 @@ class NF4Decoder:
             self.logits = torch.empty((B, self.V), device=dev, dtype=bf)
             ws = self.lib.nf4_b200_attn_decode_workspace_bytes(B, self.Hq, attn_splits)
             self.attn_ws = torch.empty((ws,), device=dev, dtype=torch.uint8)
+            self.attn_counters = torch.zeros((B * self.Hkv,), device=dev, dtype=torch.int32)
             if tp_size > 1:
                 self.cand = torch.empty((B, 2), device=dev, dtype=torch.float32)
                 self.cand_all = torch.empty((tp_size, B, 2), device=dev, dtype=torch.float32)
         self.graph = None
         self.launches_per_step = 0
+        self.gemv_events = None     # set to a list to collect (start, stop, algorithmic bytes) per GEMV launch
 
     # ------------------------------------------------------------------------------ weights
     def _make_layer(self, base: int) -> dict:
@@ -132,7 +142,8 @@ class NF4Decoder:
         wo = _seeded_normal((D, cfg.n_heads * Dh), base + 4, dev)[:, r * hq:(r + 1) * hq].contiguous()
         wg = _seeded_normal((cfg.ffn, D), base + 5, dev)
         wu = _seeded_normal((cfg.ffn, D), base + 6, dev)
-        gu = torch.cat([wg[r * self.F:(r + 1) * self.F], wu[r * self.F:(r + 1) * self.F]], dim=0)
+        # rows interleaved (gate_0, up_0, gate_1, up_1, ...) so the GEMV epilogue can apply SwiGLU
+        gu = torch.stack([wg[r * self.F:(r + 1) * self.F], wu[r * self.F:(r + 1) * self.F]], dim=1).reshape(2 * self.F, D)
         del wg, wu
         wd = _seeded_normal((D, cfg.ffn), base + 7, dev)[:, r * self.F:(r + 1) * self.F].contiguous()
         layer = {
@@ -153,17 +164,111 @@ class NF4Decoder:
     # ------------------------------------------------------------------------------ one step
     def _linear(self, x, w: NF4Weight, y, residual=None, stream=None):
         M = x.shape[0]
+        ev = self._ev_begin()
         _lib.check(self.lib.nf4_b200_gemv_fused(x.data_ptr(), M, w.K, w.packed.data_ptr(), w.absmax.data_ptr(),
                                                 w.code.data_ptr(), w.N, None,
                                                 residual.data_ptr() if residual is not None else None, y.data_ptr(),
                                                 _lib.NF4_BF16, stream), "nf4_b200_gemv_fused")
+        self._ev_end(ev, w, M)
         self._n += 1
 
     def _all_reduce(self, t):
         torch.distributed.all_reduce(t, group=self.group)
 
+    def _linear_decode(self, x, w: NF4Weight, y, residual=None, prologue=0, norm_w=None, swiglu=False, stream=None):
+        """GEMV with an optional fused prologue (RMSNorm) and epilogue (SwiGLU over interleaved gate/up
+        rows); falls back to separate glue kernels around a plain GEMV when the shape does not fit."""
+        lib, cfg, B = self.lib, self.cfg, self.B
+        ck = _lib.check
+        if swiglu and not lib.nf4_b200_gemv_decode_fits(B, w.N, w.K, prologue):
+            self._linear_decode(x, w, self.gu, prologue=prologue, norm_w=norm_w, stream=stream)
+            ck(lib.nf4_b200_silu_mul(self.gu.data_ptr(), y.data_ptr(), B, w.N // 2, 1, stream), "silu_mul")
+            self._n += 1
+            return
+        if prologue and not lib.nf4_b200_gemv_decode_fits(B, w.N, w.K, prologue):
+            if prologue == 1:
+                ck(lib.nf4_b200_rmsnorm(x.data_ptr(), norm_w.data_ptr(), self.xn.data_ptr(), B, w.K, cfg.norm_eps, stream), "rmsnorm")
+                x = self.xn
+            else:
+                ck(lib.nf4_b200_silu_mul(x.data_ptr(), self.h.data_ptr(), B, w.K, 0, stream), "silu_mul")
+                x = self.h
+            self._n += 1
+            prologue, norm_w = 0, None
+        ev = self._ev_begin()
+        ck(lib.nf4_b200_gemv_decode(x.data_ptr(), B, w.K, w.packed.data_ptr(), w.absmax.data_ptr(), w.code.data_ptr(), w.N,
+                                    residual.data_ptr() if residual is not None else None, y.data_ptr(), prologue,
+                                    norm_w.data_ptr() if norm_w is not None else None, cfg.norm_eps, 1 if swiglu else 0,
+                                    self.flags, stream),
+           "nf4_b200_gemv_decode")
+        self._ev_end(ev, w, B)
+        self._n += 1
+
+    def _ev_begin(self):
+        if self.gemv_events is None:
+            return None
+        a = torch.cuda.Event(enable_timing=True)
+        a.record()
+        return a
+
+    def _ev_end(self, a, w, M):
+        if a is not None:
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            self.gemv_events.append((a, b, w.nbytes() + 2 * M * (w.K + w.N)))
+
     def step(self) -> None:
         """One decode step on the current stream: ids_in, positions -> ids_out; positions += 1."""
+        if self.fused:
+            return self._step_fused()
+        return self._step_unfused()
+
+    def _step_fused(self) -> None:
+        cfg, lib, B = self.cfg, self.lib, self.B
+        D, Dh = cfg.d_model, cfg.head_dim
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        ck = _lib.check
+        self._n = 0
+        tp = self.tp_size > 1
+        ck(lib.nf4_b200_embed(self.ids_in.data_ptr(), self.embed.data_ptr(), self.x.data_ptr(), B, D, cfg.vocab, st), "embed")
+        self._n += 1
+        for li, layer in enumerate(self.layers):
+            self._linear_decode(self.x, layer["qkv"], self.qkv, prologue=1, norm_w=layer["norm1"], stream=st)
+            ck(lib.nf4_b200_attn_decode_fused(self.qkv.data_ptr(), self.positions.data_ptr(), self.k_cache[li].data_ptr(),
+                                              self.v_cache[li].data_ptr(), self.attn.data_ptr(), self.attn_ws.data_ptr(),
+                                              self.attn_counters.data_ptr(), B, self.Hq, self.Hkv, Dh, self.S,
+                                              self.attn_splits, cfg.rope_theta, self.flags, st), "attn_decode_fused")
+            self._n += 1
+            if tp:
+                self._linear_decode(self.attn, layer["o"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st)
+                self._all_reduce(self.part)
+                self.x, self.part = self.part, self.x
+            else:
+                self._linear_decode(self.attn, layer["o"], self.x, residual=self.x, stream=st)
+            self._linear_decode(self.x, layer["gu"], self.h, prologue=1, norm_w=layer["norm2"], swiglu=True, stream=st)
+            if tp:
+                self._linear_decode(self.h, layer["down"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st)
+                self._all_reduce(self.part)
+                self.x, self.part = self.part, self.x
+            else:
+                self._linear_decode(self.h, layer["down"], self.x, residual=self.x, stream=st)
+        self._linear_decode(self.x, self.lm_head, self.logits, prologue=1, norm_w=self.final_norm, stream=st)
+        ck(lib.nf4_b200_argmax(self.logits.data_ptr(), self.ids_out.data_ptr(), B, self.V, st), "argmax")
+        self._n += 1
+        self._finish_step()
+
+    def _finish_step(self) -> None:
+        if self.tp_size > 1:
+            # candidates (value, global index) of every rank; the first maximum in rank order wins
+            local = self.ids_out
+            self.cand[:, 0] = self.logits.gather(1, local.view(-1, 1)).view(-1).float()
+            self.cand[:, 1] = (local + self.tp_rank * self.V).float()
+            torch.distributed.all_gather_into_tensor(self.cand_all, self.cand, group=self.group)
+            best = self.cand_all[:, :, 0].argmax(dim=0)
+            self.ids_out.copy_(self.cand_all[:, :, 1].gather(0, best.view(1, -1)).view(-1).long())
+        self.positions.add_(1)
+        self.launches_per_step = self._n
+
+    def _step_unfused(self) -> None:
         cfg, lib, B = self.cfg, self.lib, self.B
         D, Dh = cfg.d_model, cfg.head_dim
         st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
@@ -191,7 +296,7 @@ class NF4Decoder:
                 self._linear(self.attn, layer["o"], self.x, residual=self.x, stream=st)
             ck(lib.nf4_b200_rmsnorm(self.x.data_ptr(), layer["norm2"].data_ptr(), self.xn.data_ptr(), B, D, cfg.norm_eps, st), "rmsnorm")
             self._linear(self.xn, layer["gu"], self.gu, stream=st)
-            ck(lib.nf4_b200_silu_mul(self.gu.data_ptr(), self.h.data_ptr(), B, self.F, st), "silu_mul")
+            ck(lib.nf4_b200_silu_mul(self.gu.data_ptr(), self.h.data_ptr(), B, self.F, 1, st), "silu_mul")
             self._n += 2
             if tp:
                 self._linear(self.h, layer["down"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st)
@@ -203,16 +308,7 @@ class NF4Decoder:
         self._linear(self.xn, self.lm_head, self.logits, stream=st)
         ck(lib.nf4_b200_argmax(self.logits.data_ptr(), self.ids_out.data_ptr(), B, self.V, st), "argmax")
         self._n += 2
-        if tp:
-            # candidates (value, global index) of every rank; the first maximum in rank order wins
-            local = self.ids_out
-            self.cand[:, 0] = self.logits.gather(1, local.view(-1, 1)).view(-1).float()
-            self.cand[:, 1] = (local + self.tp_rank * self.V).float()
-            torch.distributed.all_gather_into_tensor(self.cand_all, self.cand, group=self.group)
-            best = self.cand_all[:, :, 0].argmax(dim=0)
-            self.ids_out.copy_(self.cand_all[:, :, 1].gather(0, best.view(1, -1)).view(-1).long())
-        self.positions.add_(1)
-        self.launches_per_step = self._n
+        self._finish_step()
 
     # ------------------------------------------------------------------------------ driving it
     def capture(self, feed_back: bool = False):

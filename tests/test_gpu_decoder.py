@@ -74,20 +74,21 @@ class TorchRef:
             x = _bf(attn @ w["o"].t() + x)
             xn = _rms(x, dec.layers[li]["norm2"], cfg.norm_eps)
             gu = _bf(xn @ w["gu"].t())
-            g, u = gu[:, :dec.F], gu[:, dec.F:]
+            g, u = gu[:, 0::2], gu[:, 1::2]          # gate/up rows are interleaved in the fused matrix
             h = _bf(g / (1 + torch.exp(-g)) * u)
             x = _bf(h @ w["down"].t() + x)
         xn = _rms(x, dec.final_norm, cfg.norm_eps)
         return _bf(xn @ self.head.t())
 
 
+@pytest.mark.parametrize("fused,pdl", [(False, False), (True, False), (True, True)])
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_decode_steps_match_torch_reference(use_graph):
+def test_decode_steps_match_torch_reference(use_graph, fused, pdl):
     from nf4_b200.decoder import NF4Decoder, tiny_config
 
     torch.manual_seed(0)
     cfg = tiny_config()
-    dec = NF4Decoder(cfg, batch=2, max_seq=32, device="cuda:0", seed=3, attn_splits=3)
+    dec = NF4Decoder(cfg, batch=2, max_seq=32, device="cuda:0", seed=3, attn_splits=3, fused=fused, pdl=pdl)
     if use_graph:
         dec.capture()
     ref = TorchRef(dec)
@@ -108,6 +109,28 @@ def test_decode_steps_match_torch_reference(use_graph):
     # the caches hold what the reference holds
     torch.testing.assert_close(dec.k_cache[:, :, :, :9].float(), ref.k[:, :, :, :9], rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(dec.v_cache[:, :, :, :9].float(), ref.v[:, :, :, :9], rtol=2e-2, atol=2e-2)
+
+
+def test_fused_and_unfused_steps_agree_bitwise():
+    """Prologue fusion, the one-launch attention and programmatic dependent launch change the
+    schedule, not the arithmetic: same tokens and same logits as the kernel-per-op chain."""
+    from nf4_b200 import _lib
+    from nf4_b200.decoder import NF4Decoder, tiny_config
+
+    cfg = tiny_config(n_layers=3)
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, cfg.vocab, (2, 12), generator=g)
+    outs, logits = [], []
+    for fused, pdl, graph in [(False, False, False), (True, False, False), (True, True, False), (True, True, True)]:
+        d = NF4Decoder(cfg, batch=2, max_seq=64, seed=4, attn_splits=4, fused=fused, pdl=pdl)
+        if graph:
+            d.capture()
+        outs.append(d.generate(prompt, 10))
+        logits.append(d.logits.clone())
+    for o, l in zip(outs[1:], logits[1:]):
+        assert torch.equal(o, outs[0])
+        assert torch.equal(l, logits[0])
+    assert _lib.device_error()[0] == 0
 
 
 def test_generate_is_deterministic_and_graph_equals_eager():
@@ -140,9 +163,11 @@ def test_glue_kernels_against_torch():
     torch.testing.assert_close(y.float(), _rms(x.float(), w, 1e-5), rtol=1e-2, atol=1e-2)
     gu = torch.randn((3, 2 * 1024), device="cuda", generator=g).to(torch.bfloat16)
     h = torch.empty((3, 1024), device="cuda", dtype=torch.bfloat16)
-    _lib.check(lib.nf4_b200_silu_mul(gu.data_ptr(), h.data_ptr(), 3, 1024, st), "silu_mul")
+    _lib.check(lib.nf4_b200_silu_mul(gu.data_ptr(), h.data_ptr(), 3, 1024, 0, st), "silu_mul")
     gf = gu.float()
     torch.testing.assert_close(h.float(), _bf(torch.nn.functional.silu(gf[:, :1024]) * gf[:, 1024:]), rtol=1e-2, atol=1e-2)
+    _lib.check(lib.nf4_b200_silu_mul(gu.data_ptr(), h.data_ptr(), 3, 1024, 1, st), "silu_mul")
+    torch.testing.assert_close(h.float(), _bf(torch.nn.functional.silu(gf[:, 0::2]) * gf[:, 1::2]), rtol=1e-2, atol=1e-2)
     logits = torch.randn((4, 128256), device="cuda", generator=g).to(torch.bfloat16)
     ids = torch.empty((4,), device="cuda", dtype=torch.int64)
     _lib.check(lib.nf4_b200_argmax(logits.data_ptr(), ids.data_ptr(), 4, 128256, st), "argmax")
@@ -166,3 +191,21 @@ def test_glue_kernels_against_torch():
     _lib.check(lib.nf4_b200_gemv_fused(xx.data_ptr(), 2, 1024, packed.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(),
                                        512, None, res.data_ptr(), fused.data_ptr(), _lib.NF4_BF16, st), "gemv_fused")
     torch.testing.assert_close(fused.float(), plain.float() + res.float(), rtol=1.6e-2, atol=2e-2)
+    # decode form: RMSNorm prologue, SwiGLU prologue (halves layout) and SwiGLU epilogue (row pairs)
+    nw = torch.randn((1024,), device="cuda", generator=g).to(torch.bfloat16)
+    y1 = torch.empty_like(plain)
+    _lib.check(lib.nf4_b200_gemv_decode(xx.data_ptr(), 2, 1024, packed.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), 512,
+                                        None, y1.data_ptr(), 1, nw.data_ptr(), 1e-5, 0, 0, st), "gemv_decode rmsnorm")
+    assert torch.equal(y1, nf4_b200.matmul_4bit(_rms(xx.float(), nw, 1e-5).to(torch.bfloat16), packed.t(), quant_state=qs))
+    x2 = torch.randn((2, 2048), device="cuda", generator=g).to(torch.bfloat16)
+    y2 = torch.empty_like(plain)
+    _lib.check(lib.nf4_b200_gemv_decode(x2.data_ptr(), 2, 1024, packed.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), 512,
+                                        None, y2.data_ptr(), 2, None, 0.0, 0, 0, st), "gemv_decode silu prologue")
+    hh = _bf(torch.nn.functional.silu(x2.float()[:, :1024]) * x2.float()[:, 1024:]).to(torch.bfloat16)
+    torch.testing.assert_close(y2.float(), nf4_b200.matmul_4bit(hh, packed.t(), quant_state=qs).float(), rtol=1.6e-2, atol=1e-2)
+    y3 = torch.empty((2, 256), device="cuda", dtype=torch.bfloat16)
+    _lib.check(lib.nf4_b200_gemv_decode(xx.data_ptr(), 2, 1024, packed.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), 512,
+                                        None, y3.data_ptr(), 0, None, 0.0, 1, 0, st), "gemv_decode swiglu epilogue")
+    pf = plain.float()
+    assert torch.equal(y3, (torch.nn.functional.silu(pf[:, 0::2]) * pf[:, 1::2]).to(torch.bfloat16)) or \
+        torch.allclose(y3.float(), _bf(pf[:, 0::2] / (1 + torch.exp(-pf[:, 0::2])) * pf[:, 1::2]), rtol=1e-2, atol=1e-3)
