@@ -256,19 +256,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     // inside a group: for every K segment, every tile of the group -> one stage each.
     if (warp == CW) {
         // ------------------------------- producer warp --------------------------------------
-        // The weights do not depend on the previous kernel: the ring is filled first, the
-        // activations are fetched once the predecessor grid has finished.
-        const uint32_t x_row_bytes = (uint32_t)(p.K * 2) * (p.prologue == 2 ? 2u : 1u);
-        bool x_issued = !p.x_staged;
-        auto issue_x = [&]() {
-            griddep_wait();
-            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)p.M * x_row_bytes);
-            __syncwarp();
-            if (lane < p.M)
-                bulk_g2s(xs_u32 + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * x_row_bytes,
-                         x_row_bytes, xbar);
-            x_issued = true;
-        };
+        // The weights do not depend on the previous kernel, so this warp never waits for it; the
+        // activations are fetched by compute warp 0 once the predecessor grid has finished.
         int stage = 0, slot = 0;
         uint32_t parity = 0;
         for (int tile0 = 0; tile0 < ntiles;) {
@@ -276,7 +265,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             const int nt_here = half ? 1 : min(TG, nfull - tile0);
             for (int seg = 0; seg < p.nseg; ++seg) {
                 for (int j = 0; j < nt_here; ++j) {
-                    if (!x_issued && stage >= p.NS) issue_x();
                     mbar_wait(empty0 + slot * 8, parity ^ 1u, abort_flag, 2, stage);
                     if (lane == 0) {
                         const int row0 = r0 + (tile0 + j) * 16;
@@ -293,7 +281,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             }
             tile0 += nt_here;
         }
-        if (!x_issued) issue_x();
         return;
     }
 
@@ -315,7 +302,17 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
         }
     }
     griddep_wait();
-    if (p.x_staged) mbar_wait(xbar, 0u, abort_flag, 3, -1);
+    if (p.x_staged) {
+        if (warp == 0) {
+            const uint32_t x_row_bytes = (uint32_t)(p.K * 2) * (p.prologue == 2 ? 2u : 1u);
+            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)p.M * x_row_bytes);
+            __syncwarp();
+            if (lane < p.M)
+                bulk_g2s(xs_u32 + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * x_row_bytes,
+                         x_row_bytes, xbar);
+        }
+        mbar_wait(xbar, 0u, abort_flag, 3, -1);
+    }
 
     // ---- optional prologue on the staged activations (in place, every CTA for itself) ----------
     if (p.prologue != 0) {
