@@ -23,6 +23,39 @@ __device__ __forceinline__ uint32_t nf4_index(float v, const float* thr /*[16], 
     return i;
 }
 
+// Bucketed search.  bucket(v) = low bits of the fp32 sum v*16 + 16 + 2^23 (a monotone function of v
+// with 33 values on [-1, 1]).  If every bucket holds at most one threshold -- true whenever adjacent
+// thresholds are more than 1/16 apart, as for NF4 -- then
+//     index(v) = #{thresholds in lower buckets} + (v >= the threshold of v's own bucket),
+// which equals the threshold count exactly because bucket() is monotone.  tab[b] = (count, threshold).
+struct BucketTable { float2 tab[33]; int ok; };
+
+__device__ __forceinline__ int nf4_bucket(float v) {
+    return __float_as_int(__fmaf_rn(v, 16.0f, 8388624.0f)) & 63;
+}
+
+// called by threads 0..32 after thr[0..14] are in shared memory (followed by a barrier)
+__device__ __forceinline__ void bucket_table_build(BucketTable& bt, const float* thr, int tid) {
+    if (tid == 0) bt.ok = 1;
+    __syncthreads();
+    if (tid < 33) {
+        int below = 0, here = 0;
+        float mine = __int_as_float(0x7f800000);
+        for (int i = 0; i < 15; ++i) {
+            const int b = nf4_bucket(thr[i]);
+            if (b < tid) ++below;
+            if (b == tid) { ++here; mine = thr[i]; }
+        }
+        bt.tab[tid] = make_float2(__int_as_float(below), mine);
+        if (here > 1) bt.ok = 0;
+    }
+}
+
+__device__ __forceinline__ uint32_t nf4_index_bucketed(float v, const BucketTable& bt) {
+    const float2 e = bt.tab[nf4_bucket(v)];
+    return (uint32_t)__float_as_int(e.x) + (v >= e.y ? 1u : 0u);
+}
+
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
 
@@ -64,16 +97,13 @@ __global__ void __launch_bounds__(QTHREADS) quantize_kernel(const T* __restrict_
                                                             float* __restrict__ absmax) {
     __shared__ float s_thr[16];
     __shared__ float s_max[QTHREADS / 32];
-    __shared__ int s_zero;
+    __shared__ BucketTable s_bt;
     if (threadIdx.x < 15) s_thr[threadIdx.x] = level_threshold(code16[threadIdx.x], code16[threadIdx.x + 1]);
     if (threadIdx.x == 15) s_thr[15] = __int_as_float(0x7f800000);
-    if (threadIdx.x == 16) {
-        int z = 0;
-        for (int i = 0; i < 16; ++i) if (code16[i] == 0.0f) { z = i; break; }
-        s_zero = z;
-    }
     __syncthreads();
-    const uint32_t zero_idx = (uint32_t)s_zero;
+    bucket_table_build(s_bt, s_thr, threadIdx.x);
+    __syncthreads();
+    const bool bucketed = s_bt.ok != 0;
 
     const int64_t stride = (int64_t)gridDim.x * QTHREADS;
     // all threads of a CTA iterate the same number of times (shared-memory max needs barriers)
@@ -108,9 +138,15 @@ __global__ void __launch_bounds__(QTHREADS) quantize_kernel(const T* __restrict_
         }
         if (live) {
             uint32_t word = 0;
+            // An all-zero block divides by 1: every quotient is 0 and maps to the level nearest 0.
+            // Scales outside [2^-100, 2^100] take the compiler's fully guarded division.
+            const float dv = am == 0.0f ? 1.0f : am;
+            const bool bounded = dv >= 7.8886e-31f && dv <= 1.2676e30f;
+            const float rcp = refined_rcp(dv);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                uint32_t idx = (am == 0.0f) ? zero_idx : nf4_index(__fdiv_rn(v[i], am), s_thr);
+                const float qv = bounded ? div_rn_bounded(v[i], dv, rcp) : __fdiv_rn(v[i], dv);
+                uint32_t idx = bucketed ? nf4_index_bucketed(qv, s_bt) : nf4_index(qv, s_thr);
                 // element 2j -> high nibble of byte j; bytes are little-endian inside the word
                 const int byte = i >> 1;
                 const int shift = byte * 8 + ((i & 1) ? 0 : 4);
@@ -234,7 +270,7 @@ static int quantize_typed(const T* w, int64_t numel, int blocksize, const float*
     if (full_blocks > 0) {
         const int64_t ngroups8 = full_blocks * (blocksize / 8);
         int64_t want = (ngroups8 + QTHREADS - 1) / QTHREADS;
-        const int64_t cap = (int64_t)sm_count() * 8 * 4;
+        const int64_t cap = (int64_t)sm_count() * 8;     // 8 resident CTAs per SM; the per-CTA threshold set-up is amortised over a long loop
         const int grid = (int)(want < cap ? want : cap);
         uint32_t* p32 = reinterpret_cast<uint32_t*>(packed);
 #define NF4_Q_LAUNCH(G) quantize_kernel<T, G><<<grid, QTHREADS, 0, stream>>>(w, ngroups8, code16, p32, absmax)

@@ -132,6 +132,28 @@ def test_exhaustive_levels_against_thresholds(nf4_code_np):
     assert np.array_equal(packed.cpu().numpy(), p_ref)
 
 
+def test_division_near_thresholds_with_arbitrary_scales(nf4_code_np):
+    """The kernel divides with its own reciprocal + FMA sequence: quotients within a few ulps of every
+    decision point, for many block scales (not only 1.0), must still land on the oracle's index."""
+    import nf4_b200
+
+    rng = np.random.default_rng(42)
+    mids = ((nf4_code_np[:-1].astype(np.float64) + nf4_code_np[1:]) / 2)
+    blocks = []
+    for scale in np.concatenate([rng.uniform(1e-3, 10.0, 300), 2.0 ** rng.integers(-90, 90, 40), [0.02, 0.0625, 3.0e-30, 1.0e30]]).astype(np.float32):
+        for m in mids:
+            center = np.float32(m * np.float64(scale))
+            k = np.array([center], np.float32).view(np.int32)[0]
+            cand = np.arange(k - 31, k + 32, dtype=np.int32).view(np.float32)      # 63 neighbours
+            cand = np.clip(cand, -scale, scale)
+            blocks.append(np.concatenate([[scale], cand]).astype(np.float32))
+    w = np.concatenate(blocks)
+    packed, qs = _quant_gpu(torch.from_numpy(w))
+    p_ref, a_ref = oracle.quantize(w, nf4_code_np, 64)
+    assert np.array_equal(qs.absmax.cpu().numpy(), a_ref)
+    assert np.array_equal(packed.cpu().numpy(), p_ref)
+
+
 def test_full_size_properties(nf4_code_np):
     """Size-independent checks on the largest weight of the metric's model (lm_head 128256x4096):
     idempotence of quantize(dequantize(.)) and a checksum of per-slice checksums vs the oracle."""
