@@ -9,7 +9,7 @@
 //   warp 0   (producer)  TMA: box of 128 rows x 32 packed bytes (+16 bytes of padding per row so the
 //                        row pitch of 48 B keeps 16-byte reads of 8 consecutive rows conflict-free)
 //                        and box of TM x 64 activations (SWIZZLE_128B) -> mbarrier `full`
-//   warps 2-5 (dequant)  thread r owns weight row r: 32 bytes -> 64 bf16 through the byte->(bf16,bf16)
+//   warps 2-9 (dequant)  two threads per weight row, 16 bytes -> 32 bf16 each, through the byte->(bf16,bf16)
 //                        table, scaled by the row's fp32 absmax in fp32, rounded once, stored as
 //                        8 x 16-byte chunks at the swizzled positions of the A stage; then
 //                        fence.proxy.async + arrive on `a_ready`
@@ -40,7 +40,8 @@ int gemm_read_error(unsigned int* out4) {
     return NF4_OK;
 }
 
-constexpr int GM_THREADS = 192;          // 6 warps: producer, MMA, 4 x dequant/epilogue
+constexpr int GM_DQ_WARPS = 8;           // dequant warps: two threads per weight row (half a block each)
+constexpr int GM_THREADS = (2 + GM_DQ_WARPS) * 32;   // producer, MMA, dequant (the first 4 also run the epilogue)
 constexpr int GM_BM = 128;               // weight rows per CTA (UMMA M)
 constexpr int GM_STAGES = 3;
 constexpr int GM_PK_PITCH = 48;          // bytes per row of a packed stage (32 used)
@@ -152,7 +153,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     if (tid == 0) {
         for (int s = 0; s < GM_STAGES; ++s) {
             gm_mbar_init(full0 + 8 * s, 1);
-            gm_mbar_init(aready0 + 8 * s, 4);     // one arrival per dequant warp
+            gm_mbar_init(aready0 + 8 * s, GM_DQ_WARPS);     // one arrival per dequant warp
             gm_mbar_init(empty0 + 8 * s, 1);      // tcgen05.commit
         }
         gm_mbar_init(accdone, 1);
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     }
     if (warp >= 2) {
         // byte -> (bf16(code[hi]), bf16(code[lo])) table, one copy per lane (conflict-free lookups)
-        for (int e = warp - 2; e < 256; e += 4) {
+        for (int e = warp - 2; e < 256; e += GM_DQ_WARPS) {
             const __nv_bfloat162 h = __floats2bfloat162_rn(__ldg(p.code16 + (e >> 4)), __ldg(p.code16 + (e & 15)));
             *reinterpret_cast<uint32_t*>(lut + e * 128 + lane * 4) = *reinterpret_cast<const uint32_t*>(&h);
         }
@@ -225,25 +226,28 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         }
     } else {
         // ------------------------------------ dequant warps -------------------------------------
-        const int r = tid - 64;                 // weight row inside the tile, 0..127
+        const int t = tid - 64;                 // 0..255
+        const int r = t & 127;                  // weight row inside the tile
+        const int hsel = t >> 7;                // which half of the row's 64-block: bytes [16*hsel, 16*hsel+16)
         const int grow = n0 + r;
         const uint32_t lut_lane = gm_smem_u32(lut) + (uint32_t)lane * 4u;
         int slot = 0;
         uint32_t parity = 0;
+        float am_next = grow < p.N ? __ldg(p.absmax + (int64_t)grow * KB) : 0.0f;
         for (int kb = 0; kb < KB; ++kb) {
-            const float am = grow < p.N ? __ldg(p.absmax + (int64_t)grow * KB + kb) : 0.0f;
+            const float am = am_next;
+            if (kb + 1 < KB) am_next = grow < p.N ? __ldg(p.absmax + (int64_t)grow * KB + kb + 1) : 0.0f;
             gm_wait(full0 + 8 * slot, parity, abort_flag, 5, kb);       // packed bytes landed
             gm_wait(empty0 + 8 * slot, parity ^ 1u, abort_flag, 6, kb); // the A stage is free
-            const uint4* src = reinterpret_cast<const uint4*>(pk_base + slot * GM_PK_BYTES + r * GM_PK_PITCH);
-            const uint4 w0 = src[0], w1 = src[1];
-            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            const uint4 w4 = *reinterpret_cast<const uint4*>(pk_base + slot * GM_PK_BYTES + r * GM_PK_PITCH + hsel * 16);
+            const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
             uint8_t* const arow = a_base + slot * GM_A_BYTES + r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {       // 16-byte chunk c = 8 weights = 4 packed bytes = one word
+            for (int c = 0; c < 4; ++c) {       // 16-byte chunk = 8 weights = 4 packed bytes = one word
                 uint32_t out[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint32_t byte = (words[c] >> (8 * j)) & 0xffu;
+                    const uint32_t byte = __byte_perm(words[c], 0u, 0x4440 | j);
                     uint32_t pair;
                     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(pair) : "r"(lut_lane + byte * 128u));
                     const float lo = __uint_as_float(pair << 16) * am;
@@ -251,7 +255,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
                     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
                     out[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
-                *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = make_uint4(out[0], out[1], out[2], out[3]);
+                const int chunk = hsel * 4 + c;
+                *reinterpret_cast<uint4*>(arow + ((chunk ^ (r & 7)) << 4)) = make_uint4(out[0], out[1], out[2], out[3]);
             }
             // generic-proxy stores must be visible to the tensor core (async proxy)
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -259,6 +264,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
             if (lane == 0) gm_mbar_arrive(aready0 + 8 * slot);
             if (++slot == GM_STAGES) { slot = 0; parity ^= 1u; }
         }
+        if (warp >= 6) goto done;               // the epilogue needs one warp per TMEM lane quarter
         // ------------------------------------ epilogue ------------------------------------------
         gm_wait(accdone, 0u, abort_flag, 8, KB);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -286,6 +292,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
+done:
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
