@@ -162,13 +162,19 @@ def run_kernel(args):
         del w
     x = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
     y = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+    # gemv: the fused GEMV whatever M (up to 16); gemm: the library's dispatch, with its split-K scratch
+    need = lib.nf4_b200_linear_workspace_bytes(M, N, K, _lib.NF4_BF16) if args.kernel == "gemm" else 0
+    scratch = torch.zeros((max(need, 16),), device="cuda", dtype=torch.uint8)
 
     def launch_all():
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         for p, qs in ws:
-            if args.kernel in ("gemv", "gemm"):
+            if args.kernel == "gemv":
+                rc = lib.nf4_b200_gemv(x.data_ptr(), M, K, p.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N,
+                                       None, y.data_ptr(), _lib.NF4_BF16, st)
+            elif args.kernel == "gemm":
                 rc = lib.nf4_b200_linear(x.data_ptr(), M, K, p.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N, 64,
-                                         None, y.data_ptr(), _lib.NF4_BF16, None, 0, st)
+                                         None, y.data_ptr(), _lib.NF4_BF16, scratch.data_ptr(), scratch.numel(), st)
             elif args.kernel == "dequantize":
                 rc = lib.nf4_b200_dequantize(p.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N * K, 64,
                                              deq.data_ptr(), _lib.NF4_BF16, st)
@@ -183,11 +189,20 @@ def run_kernel(args):
     for _ in range(max(1, args.warmup)):
         launch_all()
     torch.cuda.synchronize()
+    run = launch_all
+    if args.kernel in ("gemv", "gemm"):
+        # one CUDA graph of the nbuf launches: small shapes would otherwise time the host's launch rate
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launch_all()
+        run = graph.replay
+        run()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ts = []
     for _ in range(max(1, args.steps)):
         e0.record()
-        launch_all()
+        run()
         e1.record()
         torch.cuda.synchronize()
         ts.append(e0.elapsed_time(e1) * 1e3 / nbuf)

@@ -58,6 +58,7 @@ bool gemv_supported(int64_t M, int64_t K, int64_t N, int blocksize, int dtype, c
                     const void* absmax);
 bool gemm_supported(int64_t M, int64_t K, int64_t N, int blocksize, int dtype, const void* x, const void* packed,
                     const void* absmax, const void* y);
+int gemm_min_m();
 
 }  // namespace nf4
 
@@ -76,8 +77,8 @@ extern "C" int nf4_b200_last_error(char* buf, int buflen) {
 }
 
 extern "C" int64_t nf4_b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype) {
-    (void)M; (void)N; (void)K; (void)dtype;
-    return 0;
+    if (dtype != NF4_BF16 || M < nf4::gemm_min_m() || K % 64 != 0) return 0;
+    return nf4_b200_gemm_workspace_bytes(M, N, K);
 }
 
 extern "C" int nf4_b200_linear(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
@@ -87,9 +88,10 @@ extern "C" int nf4_b200_linear(const void* x, int64_t M, int64_t K, const uint8_
     NF4_REQUIRE(dtype == NF4_F32 || dtype == NF4_F16 || dtype == NF4_BF16, NF4_ERR_ARG, "linear: unknown dtype code %d", dtype);
     if (M == 0 || N == 0) return NF4_OK;
     NF4_REQUIRE(x && packed && absmax && code16 && y, NF4_ERR_ARG, "linear: null pointer");
-    if (gemv_supported(M, K, N, blocksize, dtype, x, packed, absmax))
+    const bool gemm_ok = gemm_supported(M, K, N, blocksize, dtype, x, packed, absmax, y);
+    if (!gemm_ok && gemv_supported(M, K, N, blocksize, dtype, x, packed, absmax))
         return nf4_b200_gemv(x, M, K, packed, absmax, code16, N, bias, y, dtype, stream);
-    if (gemm_supported(M, K, N, blocksize, dtype, x, packed, absmax, y))
+    if (gemm_ok)
         return nf4_b200_gemm(x, M, K, packed, absmax, code16, N, bias, y, dtype, workspace, workspace_bytes, stream);
     return nf4_b200_linear_generic(x, M, K, packed, absmax, code16, N, blocksize, bias, y, dtype, stream);
 }

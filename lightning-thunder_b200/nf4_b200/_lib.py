@@ -30,6 +30,9 @@ SIGNATURES = {
     "nf4_b200_gemv": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "nf4_b200_gemm": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int,
                                _c_ptr, _c_i64, _c_ptr]),
+    "nf4_b200_gemm_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64]),
+    "nf4_b200_gemm_decode": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int,
+                                      _c_ptr, _c_i64, _c_int, _c_ptr]),
     "nf4_b200_linear_generic": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr,
                                          _c_ptr, _c_int, _c_ptr]),
     "nf4_b200_device_error": (_c_int, [_c_ptr]),

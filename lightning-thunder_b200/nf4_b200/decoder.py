@@ -71,7 +71,8 @@ def _seeded_normal(shape, seed: int, device, std=0.02) -> torch.Tensor:
 
 class NF4Decoder:
     def __init__(self, cfg: DecoderConfig, batch: int, max_seq: int, device="cuda:0", seed: int = 0, tp_rank: int = 0,
-                 tp_size: int = 1, group=None, attn_splits: int | None = None, fused: bool = True, pdl: bool = True):
+                 tp_size: int = 1, group=None, attn_splits: int | None = None, fused: bool = True, pdl: bool = True,
+                 tensor_core_from: int = 9):
         assert cfg.head_dim == 128, "the attention kernel is written for head_dim 128"
         assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.ffn % (64 * tp_size) == 0
         assert cfg.vocab % tp_size == 0 and batch <= 16
@@ -88,6 +89,9 @@ class NF4Decoder:
         # the tail of its predecessor).
         self.fused = fused
         self.flags = 1 if (fused and pdl) else 0
+        # from this many sequences on, the fused step's linears run on the tensor-core kernel (K split over
+        # thread blocks, residual / SwiGLU epilogues) with RMSNorm as a separate small kernel before it
+        self.tensor_core = fused and batch >= tensor_core_from
         self.Hq = cfg.n_heads // tp_size
         self.Hkv = cfg.n_kv_heads // tp_size
         self.F = cfg.ffn // tp_size
@@ -122,6 +126,9 @@ class NF4Decoder:
             ws = self.lib.nf4_b200_attn_decode_workspace_bytes(B, self.Hq, attn_splits)
             self.attn_ws = torch.empty((ws,), device=dev, dtype=torch.uint8)
             self.attn_counters = torch.zeros((B * self.Hkv,), device=dev, dtype=torch.int32)
+            shapes = [(self.lm_head.N, self.lm_head.K)] + [(l[k].N, l[k].K) for l in self.layers[:1] for k in ("qkv", "o", "gu", "down")]
+            gws = max(self.lib.nf4_b200_gemm_workspace_bytes(B, n, k) for n, k in shapes) if self.tensor_core else 0
+            self.gemm_ws = torch.zeros((max(gws, 16),), device=dev, dtype=torch.uint8)   # zero once; the kernels keep it so
             if tp_size > 1:
                 self.cand = torch.empty((B, 2), device=dev, dtype=torch.float32)
                 self.cand_all = torch.empty((tp_size, B, 2), device=dev, dtype=torch.float32)
@@ -180,6 +187,23 @@ class NF4Decoder:
         rows); falls back to separate glue kernels around a plain GEMV when the shape does not fit."""
         lib, cfg, B = self.lib, self.cfg, self.B
         ck = _lib.check
+        if self.tensor_core:
+            if prologue == 1:
+                ck(lib.nf4_b200_rmsnorm(x.data_ptr(), norm_w.data_ptr(), self.xn.data_ptr(), B, w.K, cfg.norm_eps, stream), "rmsnorm")
+                x = self.xn
+                self._n += 1
+            elif prologue == 2:
+                ck(lib.nf4_b200_silu_mul(x.data_ptr(), self.h.data_ptr(), B, w.K, 0, stream), "silu_mul")
+                x = self.h
+                self._n += 1
+            ev = self._ev_begin()
+            ck(lib.nf4_b200_gemm_decode(x.data_ptr(), B, w.K, w.packed.data_ptr(), w.absmax.data_ptr(), w.code.data_ptr(), w.N,
+                                        residual.data_ptr() if residual is not None else None, y.data_ptr(), 1 if swiglu else 0,
+                                        self.gemm_ws.data_ptr(), self.gemm_ws.numel(), self.flags, stream),
+               "nf4_b200_gemm_decode")
+            self._ev_end(ev, w, B)
+            self._n += 1
+            return
         if swiglu and not lib.nf4_b200_gemv_decode_fits(B, w.N, w.K, prologue):
             self._linear_decode(x, w, self.gu, prologue=prologue, norm_w=norm_w, stream=stream)
             ck(lib.nf4_b200_silu_mul(self.gu.data_ptr(), y.data_ptr(), B, w.N // 2, 1, stream), "silu_mul")

@@ -176,6 +176,27 @@ def dequantize_4bit(A: torch.Tensor, quant_state: QuantState = None, absmax=None
     return out
 
 
+_WORKSPACES: dict = {}
+
+
+def _linear_workspace(lib, M: int, N: int, K: int, dtype_code: int, device, stream_ptr):
+    """Zero-initialised split-K scratch for (device, stream), grown on demand.  The kernels return it to
+    its initial state, so one buffer serves every call on that stream.  While a CUDA graph is being
+    captured no new buffer is created (it would belong to the graph's pool): the call then runs without
+    a K split unless a large enough buffer already exists."""
+    need = int(lib.nf4_b200_linear_workspace_bytes(M, N, K, dtype_code))
+    if need == 0:
+        return None, 0
+    key = (torch.device(device).index, stream_ptr.value if hasattr(stream_ptr, "value") else int(stream_ptr or 0))
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            return None, 0
+        ws = torch.zeros((max(need, 1 << 22),), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws, ws.numel()
+
+
 def linear_nf4(x: torch.Tensor, packed: torch.Tensor, bias, absmax: torch.Tensor, code: torch.Tensor, blocksize: int,
                shape: Sequence[int], out=None) -> torch.Tensor:
     """y = x @ dequant(W).T + bias for W of logical `shape` = (N, K) stored as packed/absmax/code."""
@@ -196,10 +217,12 @@ def linear_nf4(x: torch.Tensor, packed: torch.Tensor, bias, absmax: torch.Tensor
         if out is None:
             out = torch.empty((*x.shape[:-1], N), dtype=x.dtype, device=x.device)
         lib = _lib.load()
+        stream = _stream_ptr(x.device)
+        ws, ws_bytes = _linear_workspace(lib, M, N, K, _DTYPE_CODE[x.dtype], x.device, stream) if int(blocksize) == 64 else (None, 0)
         _lib.check(
             lib.nf4_b200_linear(x2.data_ptr(), M, K, packed.data_ptr(), absmax.data_ptr(), code.data_ptr(), N,
                                 int(blocksize), bias.data_ptr() if bias is not None else None, out.data_ptr(),
-                                _DTYPE_CODE[x.dtype], None, 0, _stream_ptr(x.device)),
+                                _DTYPE_CODE[x.dtype], ws.data_ptr() if ws is not None else None, ws_bytes, stream),
             "nf4_b200_linear",
         )
     return out

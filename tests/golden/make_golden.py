@@ -32,7 +32,7 @@ def config1(seed_w=1234, seed_x=4321):
     wb = bf16_bits(w)
     packed, absmax = oracle.quantize(wb, CODE, 64)
     deq = oracle.dequantize(packed, absmax, CODE, N * K, 64, out="bf16")
-    y = oracle.linear_bf16(bf16_bits(x), packed, absmax, CODE, N, K, 64)
+    y = oracle.linear_bf16(bf16_bits(x), packed, absmax, CODE, N, K, 64, mode=oracle.GEMV_MODE)
     return {
         "name": "config1",
         "seed_w": seed_w,

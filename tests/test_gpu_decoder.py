@@ -10,14 +10,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _deq(w):
+def _deq(w, round_w=False):
     import nf4_b200
 
     qs = nf4_b200.QuantState(w.absmax, shape=(w.N, w.K), code=w.code, blocksize=64, dtype=torch.bfloat16)
     # GEMV numerics: levels rounded to bf16, scaled by the fp32 absmax, no rounding of the product
     idx = torch.stack([w.packed.view(-1) >> 4, w.packed.view(-1) & 15], 1).view(-1).long()
     lv = qs.code.to(torch.bfloat16).float()[idx]
-    return (lv.view(-1, 64) * w.absmax.view(-1, 1)).view(w.N, w.K)
+    wd = (lv.view(-1, 64) * w.absmax.view(-1, 1)).view(w.N, w.K)
+    # tensor-core numerics: the product is rounded to bf16 before the matrix multiply
+    return wd.to(torch.bfloat16).float() if round_w else wd
 
 
 def _bf(t):
@@ -42,8 +44,9 @@ def _rope(x, pos, theta):
 class TorchRef:
     def __init__(self, dec):
         self.dec, self.cfg = dec, dec.cfg
-        self.layers = [{k: _deq(l[k]) for k in ("qkv", "o", "gu", "down")} for l in dec.layers]
-        self.head = _deq(dec.lm_head)
+        tc = dec.tensor_core
+        self.layers = [{k: _deq(l[k], tc) for k in ("qkv", "o", "gu", "down")} for l in dec.layers]
+        self.head = _deq(dec.lm_head, tc)
         L, B, S = self.cfg.n_layers, dec.B, dec.S
         self.k = torch.zeros((L, B, dec.Hkv, S, 128), device=dec.dev)
         self.v = torch.zeros((L, B, dec.Hkv, S, 128), device=dec.dev)
@@ -109,6 +112,36 @@ def test_decode_steps_match_torch_reference(use_graph, fused, pdl):
     # the caches hold what the reference holds
     torch.testing.assert_close(dec.k_cache[:, :, :, :9].float(), ref.k[:, :, :, :9], rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(dec.v_cache[:, :, :, :9].float(), ref.v[:, :, :, :9], rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_batched_decode_on_tensor_cores(use_graph):
+    """More than 8 sequences: the step's linears run on the tcgen05 kernel (K split over thread blocks,
+    residual and SwiGLU epilogues, programmatic dependent launch)."""
+    from nf4_b200 import _lib
+    from nf4_b200.decoder import NF4Decoder, tiny_config
+
+    cfg = tiny_config()
+    B = 12
+    dec = NF4Decoder(cfg, batch=B, max_seq=16, device="cuda:0", seed=5)
+    assert dec.tensor_core
+    if use_graph:
+        dec.capture()
+    ref = TorchRef(dec)
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, cfg.vocab, (B, 4), generator=g).cuda()
+    dec.reset()
+    agree = 0
+    for t in range(toks.shape[1]):
+        pos = dec.positions.clone().long()
+        dec.ids_in.copy_(toks[:, t])
+        dec.run_step()
+        torch.cuda.synchronize()
+        want = ref.step(toks[:, t], pos)
+        torch.testing.assert_close(dec.logits.float(), want, rtol=3e-2, atol=3e-2)
+        agree += int((dec.ids_out == want.argmax(-1)).sum())
+    assert agree >= B * toks.shape[1] - 3
+    assert _lib.device_error()[0] == 0
 
 
 def test_fused_and_unfused_steps_agree_bitwise():

@@ -16,15 +16,15 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 1.6e-2, 1e-2
 
 
-# M > 16 in bf16 runs the tcgen05 GEMM (weights = the GEMV's weights rounded to bf16); fp16 runs
-# the GEMV kernel once per slab of 16 activation rows.
+# M > 8 in bf16 runs the tcgen05 GEMM (weights = the GEMV's weights rounded to bf16); fp16 runs
+# the GEMV kernel once per slab of 16 activation rows.  NF4_GEMM_MIN_M=17 keeps M = 9..16 on the GEMV.
 GEMM_ORACLE_MODE = oracle.GEMM_MODE
 
 
 def _oracle_linear(x_cpu, packed_np, absmax_np, code, N, K, bias_cpu=None, mode=None, blocksize=64):
     if x_cpu.dtype == torch.bfloat16:
         if mode is None:
-            mode = oracle.GEMV_MODE if x_cpu.shape[0] <= 16 else GEMM_ORACLE_MODE
+            mode = oracle.linear_mode_for(x_cpu.shape[0])
         y = oracle.linear_bf16(bf16_bits(x_cpu), packed_np, absmax_np, code, N, K, blocksize,
                                None if bias_cpu is None else bf16_bits(bias_cpu), mode=mode)
         return bits_to_bf16(y).float()
@@ -74,9 +74,10 @@ def test_gemv_every_plan(nf4_code_np, plan, monkeypatch):
     """Forces each (rows-per-warp, K-split) variant of the GEMV on the same problem."""
     monkeypatch.setenv("NF4_GEMV_KERNEL", "direct")
     monkeypatch.setenv("NF4_GEMV_PLAN", plan)
+    monkeypatch.setenv("NF4_GEMM_MIN_M", "17")
     w = seeded_weight((1500, 2048), 17)
     for M in (1, 5, 12):
-        _check(seeded_act((M, 2048), M + 100), w, nf4_code_np)
+        _check(seeded_act((M, 2048), M + 100), w, nf4_code_np, mode=oracle.GEMV_MODE)
 
 
 @pytest.mark.parametrize("kernel", ["direct", "staged"])
@@ -88,8 +89,9 @@ def test_gemv_both_kernels(nf4_code_np, kernel, M, N, K, monkeypatch):
     from nf4_b200 import _lib
 
     monkeypatch.setenv("NF4_GEMV_KERNEL", kernel)
+    monkeypatch.setenv("NF4_GEMM_MIN_M", "17")
     w = seeded_weight((N, K), N + 3 * K)
-    _check(seeded_act((M, K), M), w, nf4_code_np, bias_cpu=seeded_act((N,), 2))
+    _check(seeded_act((M, K), M), w, nf4_code_np, bias_cpu=seeded_act((N,), 2), mode=oracle.GEMV_MODE)
     assert _lib.device_error()[0] == 0
 
 
@@ -99,9 +101,10 @@ def test_gemv_staged_group_sizes(nf4_code_np, tg, monkeypatch):
 
     monkeypatch.setenv("NF4_GEMV_KERNEL", "staged")
     monkeypatch.setenv("NF4_GEMV_TG", tg)
+    monkeypatch.setenv("NF4_GEMM_MIN_M", "17")
     w = seeded_weight((128256 // 8, 4096), 5)     # 108 rows per CTA: several groups, ragged last tile
     for M in (1, 6, 16):
-        _check(seeded_act((M, 4096), M + 50), w, nf4_code_np)
+        _check(seeded_act((M, 4096), M + 50), w, nf4_code_np, mode=oracle.GEMV_MODE)
     assert _lib.device_error()[0] == 0
 
 
@@ -201,3 +204,82 @@ def test_linearity_at_full_size(nf4_code_np):
     ref_col = (qs.code[(packed.view(N, K // 2)[:, 617].int() >> 4).long()].to(torch.bfloat16).float()
                * qs.absmax.view(N, K // 64)[:, 1234 // 64])
     torch.testing.assert_close(col.float(), ref_col, rtol=8e-3, atol=1e-6)
+
+
+def _gemm_ref(x, packed, qs, N, K):
+    """fp32 matmul on the GEMM's own weight definition bf16(bf16(level) * absmax); torch is only the checker."""
+    idx = torch.stack([packed.view(-1) >> 4, packed.view(-1) & 15], 1).view(-1).long()
+    wd = (qs.code.to(torch.bfloat16).float()[idx].view(-1, 64) * qs.absmax.view(-1, 1)).view(N, K).to(torch.bfloat16)
+    return x.float() @ wd.float().t()
+
+
+@pytest.mark.parametrize("splits", ["1", "2", "3", "7"])
+@pytest.mark.parametrize("M,N,K", [(9, 256, 1024), (16, 4096, 4096), (16, 1280, 8192), (40, 300, 2048), (130, 512, 1024)])
+def test_gemm_split_k(nf4_code_np, splits, M, N, K, monkeypatch):
+    """K cut into ranges over thread blocks (partial sums parked in the workspace, last arrival adds
+    them in range order): every split count gives the oracle's result, twice in a row on one workspace."""
+    import nf4_b200
+    from nf4_b200 import _lib
+
+    monkeypatch.setenv("NF4_GEMM_SPLITS", splits)
+    w = seeded_weight((N, K), N + K + 1)
+    x = seeded_act((M, K), M + 2)
+    y1 = _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9))
+    y2 = _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9))
+    assert torch.equal(y1, y2)
+    assert _lib.device_error()[0] == 0
+
+
+def test_gemm_planned_split_matches_unsplit(nf4_code_np, monkeypatch):
+    """The library's own split plan for a decode shape against the same call with the split off: the
+    sums differ only in fp32 association."""
+    import nf4_b200
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    M, N, K = 16, 4096, 4096
+    assert lib.nf4_b200_gemm_workspace_bytes(M, N, K) > 0          # 32 weight tiles: a split is planned
+    assert lib.nf4_b200_gemm_workspace_bytes(M, 128256, K) == 0    # 1002 tiles: none
+    w = seeded_weight((N, K), 5).cuda()
+    x = seeded_act((M, K), 6).cuda()
+    packed, qs = nf4_b200.quantize_4bit(w)
+    y_split = nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs)
+    monkeypatch.setenv("NF4_GEMM_SPLITS", "1")
+    y_one = nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs)
+    torch.testing.assert_close(y_split.float(), y_one.float(), rtol=8e-3, atol=2e-3)
+    torch.testing.assert_close(y_split.float(), _gemm_ref(x, packed, qs, N, K), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("flags", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(16, 1024, 2048), (12, 384, 512), (32, 4096, 1024)])
+def test_gemm_decode_epilogues(nf4_code_np, flags, M, N, K):
+    """nf4_b200_gemm_decode: residual epilogue (aliasing y) and SwiGLU over (gate, up) row pairs, with
+    and without programmatic dependent launch, with and without a workspace."""
+    import ctypes
+
+    import nf4_b200
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    w = seeded_weight((N, K), N * 3 + K).cuda()
+    x = seeded_act((M, K), M + 11).cuda()
+    res = seeded_act((M, N), 12).cuda()
+    packed, qs = nf4_b200.quantize_4bit(w)
+    ref = _gemm_ref(x, packed, qs, N, K)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    need = lib.nf4_b200_gemm_workspace_bytes(M, N, K)
+    for ws in (None, torch.zeros((max(need, 16),), dtype=torch.uint8, device="cuda")):
+        wp, wb = (ws.data_ptr(), ws.numel()) if ws is not None else (None, 0)
+        y = res.clone()
+        _lib.check(lib.nf4_b200_gemm_decode(x.data_ptr(), M, K, packed.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N,
+                                            y.data_ptr(), y.data_ptr(), 0, wp, wb, flags, st), "gemm_decode")
+        torch.testing.assert_close(y.float(), ref + res.float(), rtol=RTOL, atol=ATOL)
+        h = torch.empty((M, N // 2), dtype=torch.bfloat16, device="cuda")
+        for _ in range(2):
+            _lib.check(lib.nf4_b200_gemm_decode(x.data_ptr(), M, K, packed.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(),
+                                                N, None, h.data_ptr(), 1, wp, wb, flags, st), "gemm_decode")
+        gu = ref.to(torch.bfloat16).float()
+        href = torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]
+        torch.testing.assert_close(h.float(), href, rtol=3e-2, atol=1e-2)
+    torch.cuda.synchronize()
+    assert _lib.device_error()[0] == 0

@@ -113,7 +113,7 @@ def test_config1_golden(nf4_code_np):
     assert packed.reshape(-1)[:32].tobytes().hex() == g["packed_head_hex"]
     deq = oracle.dequantize(packed, absmax, nf4_code_np, N * K, 64, out="bf16")
     assert sha256(deq) == g["dequant_bf16_sha256"]
-    y = oracle.linear_bf16(bf16_bits(x), packed, absmax, nf4_code_np, N, K, 64)   # 16 rows -> fused-GEMV regime
+    y = oracle.linear_bf16(bf16_bits(x), packed, absmax, nf4_code_np, N, K, 64, mode=oracle.GEMV_MODE)   # the pinned regime
     assert sha256(y) == g["y_bf16_sha256"]
     xs = x.float().numpy().astype(np.float64)[:2]
     # regime "dequantize then matmul": float64 matmul on the bf16-rounded dequantised weight
