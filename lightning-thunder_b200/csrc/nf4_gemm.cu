@@ -49,23 +49,28 @@ int gemm_read_error(unsigned int* out4) {
     return NF4_OK;
 }
 
-constexpr int GM_DQ_WARPS = 8;           // dequant warps: two threads per weight row (half a block each)
+constexpr int GM_DQ_WARPS = 16;          // dequant warps: four threads per weight row (a quarter block each)
 constexpr int GM_THREADS = (3 + GM_DQ_WARPS) * 32;   // activation producer, MMA, dequant (the first 4 also run the epilogue), weight producer
 constexpr int GM_WPRODUCER = 2 + GM_DQ_WARPS;        // warp index of the weight producer
 constexpr int GM_BM = 128;               // weight rows per CTA (UMMA M)
-constexpr int GM_STAGES = 4;
-constexpr int GM_A_COLS = 32;            // TMEM columns of one weight stage: 64 bf16 per row, two per column
-constexpr int GM_WSTAGES = 3;            // packed-weight stages, each GM_WKB K blocks deep
+constexpr int GM_MAX_STAGES = 4;         // activation stages (= weight stages in TMEM): 4, or 3 for 256-row tiles
+constexpr int GM_A_COLS = 32;            // TMEM columns of one K block of weights: 64 bf16 per row, two per column
+constexpr int GM_GROUPS = 2;             // weight groups (GM_WKB K blocks each) in TMEM: one converts while one multiplies
+constexpr int GM_A_COL0 = 256;           // accumulator in TMEM columns [0, 256), weight groups in [256, 512)
+constexpr int GM_TMEM_COLS = 512;
+constexpr int GM_MAX_WSTAGES = 5;        // packed-weight stages, each GM_WKB K blocks deep: 5, or 3 for 256-row tiles
 constexpr int GM_WKB = 4;                // K blocks per packed-weight stage: 4 x 32 B = one 128-byte swizzle row
 constexpr int GM_PK_BYTES = GM_BM * 128; // one packed-weight stage
-constexpr int GM_LUT_BYTES = 256 * 128;  // byte -> (bf16,bf16), one copy per lane
-constexpr int GM_MIN_SMEM = 80 * 1024;   // request at least this much: at most two CTAs (2 x 256 TMEM columns) per SM
-constexpr int GM_MAX_CTAS_SPLIT = 296;   // split K until about two CTAs per SM exist
+constexpr int GM_AM_BYTES = GM_BM * 16;  // its absmax: 4 floats per row
+constexpr uint32_t GM_LUT_WINDOW = 65536;  // byte -> (fp32, fp32): 256 entries x 32 lanes x 8 B, 64 KB aligned in the shared window
+constexpr uint32_t GM_LOW_BASE = 2048;     // buffers below the window start here (the dynamic region starts at or below it)
+constexpr int GM_SM_TARGET = 148;        // split K until about one CTA per SM exists
 constexpr unsigned long long GM_WAIT_LIMIT_NS = 200ull * 1000 * 1000;
 
 struct alignas(64) GemmParams {
     CUtensorMap wmap;     // packed codes uint8 [N][K/2], box 128 B x 128 rows, SWIZZLE_128B
     CUtensorMap xmap;     // activations bf16 [M][K], box 64 x TM, SWIZZLE_128B
+    CUtensorMap amap;     // absmax fp32 [N][K/64], box 4 x 128 (used when K/64 is a multiple of 4)
     const float* absmax;
     const float* code16;
     const void* bias;
@@ -75,10 +80,16 @@ struct alignas(64) GemmParams {
     unsigned* counters;   // split K: one arrival counter per (weight tile, activation tile); zero between launches
     int M, N, K, KB;
     int TM;               // activation rows per CTA: multiple of 16, 32..256
-    int tmem_cols;        // power of two >= TM + GM_STAGES * GM_A_COLS
     int splits;           // K is cut into this many ranges, one CTA each
     int epilogue;         // 0: y[m][n];  1: rows are (gate, up) pairs, y[m][n/2] = silu(gate) * up
     int pdl;              // programmatic dependent launch: weights may be fetched before the upstream grid ends
+    int stages, wstages;  // ring depths
+    // shared-window addresses (the table takes [64K, 128K); the host lays the rest out around it)
+    uint32_t b_addr[GM_MAX_STAGES];    // activation stages, 1024-byte aligned
+    uint32_t w_addr[GM_MAX_WSTAGES];   // packed-weight stages, 1024-byte aligned
+    uint32_t am_addr[GM_MAX_WSTAGES];  // absmax of a packed stage: 128 rows x 4 floats
+    int am_tma;                        // absmax travels with the packed weights (else it is loaded from global)
+    uint32_t bar_addr;                 // mbarriers + 16 bytes of flags
 };
 
 __device__ __forceinline__ uint32_t gm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -105,11 +116,14 @@ __device__ __forceinline__ unsigned long long gm_global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ void gm_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int iter) {
-    if (gm_mbar_try_wait(bar, parity)) return;
+// Bounded wait.  The hot path is a plain poll of the barrier; only a wait that has already lasted thousands
+// of polls starts reading the timer and the CTA's abort flag (both are slow enough to show in a hand-off).
+__device__ __noinline__ void gm_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int iter) {
     if (*abort_flag) return;
     const unsigned long long t0 = gm_global_ns();
-    while (!gm_mbar_try_wait(bar, parity)) {
+    while (true) {
+        for (int spin = 0; spin < 256; ++spin)
+            if (gm_mbar_try_wait(bar, parity)) return;
         if (*abort_flag) return;
         if (gm_global_ns() - t0 > GM_WAIT_LIMIT_NS) {
             *abort_flag = 1;
@@ -122,9 +136,39 @@ __device__ __forceinline__ void gm_wait(uint32_t bar, uint32_t parity, volatile 
         }
     }
 }
+__device__ __forceinline__ void gm_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int iter) {
+#pragma unroll 1
+    for (int spin = 0; spin < 4096; ++spin)
+        if (gm_mbar_try_wait(bar, parity)) return;
+    gm_wait_slow(bar, parity, abort_flag, code, iter);
+}
 __device__ __forceinline__ void gm_tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// table lookup: the packed byte `sel` of `word` becomes bits 8..15 of the 64 KB aligned window address
+template <int SEL>
+__device__ __forceinline__ void gm_lookup(uint32_t word, uint32_t window_lane, float& first, float& second) {
+    const uint32_t addr = __byte_perm(word, window_lane, 0x7604 | (SEL << 4));
+    asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(first), "=f"(second) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t gm_scale_pack(float first, float second, float am) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(first * am, second * am);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// D[tmem] (+)= A[tmem] . B[smem]^T, 128 x N x 16, bf16 operands, fp32 accumulator
+__device__ __forceinline__ void gm_mma(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the mbarrier gets one arrival once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void gm_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // 32 lanes x 16 columns of fp32 from tensor memory into 16 registers per thread
@@ -164,33 +208,42 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int TM = p.TM;
     const int b_bytes = TM * 128;
+    const int NS = p.stages, NW = p.wstages;
 
-    // shared-memory map (all stage bases 1024-byte aligned)
-    uint8_t* const b_base = smem;                                      // GM_STAGES x TM*128
-    uint8_t* const pk_base = b_base + GM_STAGES * b_bytes;             // GM_WSTAGES x 16 KB
-    uint8_t* const lut = pk_base + GM_WSTAGES * GM_PK_BYTES;           // 32 KB
-    uint64_t* const bars = reinterpret_cast<uint64_t*>(lut + GM_LUT_BYTES);
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+    // The host laid the buffers out in shared-window addresses around the table's window [64K, 128K),
+    // assuming the dynamic region starts at or below GM_LOW_BASE.
+    const uint32_t s0 = gm_smem_u32(smem);
+    if (s0 > GM_LOW_BASE) {
+        if (tid == 0 && atomicCAS(&g_gemm_error[0], 0u, 10u) == 0u) g_gemm_error[1] = s0;
+        return;
+    }
+    const uint32_t full0 = p.bar_addr, bempty0 = full0 + 8 * GM_MAX_STAGES, aready0 = bempty0 + 8 * GM_MAX_STAGES,
+                   aempty0 = aready0 + 8 * GM_GROUPS, accdone = aempty0 + 8 * GM_GROUPS, wfull0 = accdone + 8,
+                   wempty0 = wfull0 + 8 * GM_MAX_WSTAGES, flags0 = wempty0 + 8 * GM_MAX_WSTAGES;
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + (flags0 - s0));
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* const last_flag = abort_flag + 1;
-    const uint32_t full0 = gm_smem_u32(bars), aready0 = full0 + 8 * GM_STAGES, empty0 = full0 + 16 * GM_STAGES,
-                   accdone = full0 + 24 * GM_STAGES, wfull0 = accdone + 8, wempty0 = wfull0 + 8 * GM_WSTAGES;
 
     const int n0 = blockIdx.x * GM_BM;
     const int mtile = blockIdx.y / p.splits;
     const int split = blockIdx.y - mtile * p.splits;
     const int m0 = mtile * TM;
     // this CTA's range of 64-element K blocks (never empty: splits <= KB)
-    const int kb_begin = (int)((int64_t)p.KB * split / p.splits);
-    const int kb_end = (int)((int64_t)p.KB * (split + 1) / p.splits);
+    // (whole groups of GM_WKB blocks when absmax comes by TMA: its box must start 16-byte aligned)
+    const int units = p.am_tma ? p.KB / GM_WKB : p.KB, unit = p.am_tma ? GM_WKB : 1;
+    const int kb_begin = (int)((int64_t)units * split / p.splits) * unit;
+    const int kb_end = (int)((int64_t)units * (split + 1) / p.splits) * unit;
 
     if (tid == 0) {
-        for (int s = 0; s < GM_STAGES; ++s) {
+        for (int s = 0; s < NS; ++s) {
             gm_mbar_init(full0 + 8 * s, 1);
-            gm_mbar_init(aready0 + 8 * s, GM_DQ_WARPS);   // one arrival per dequant warp
-            gm_mbar_init(empty0 + 8 * s, 1);              // tcgen05.commit
+            gm_mbar_init(bempty0 + 8 * s, 1);             // tcgen05.commit after the K block's MMAs
         }
-        for (int s = 0; s < GM_WSTAGES; ++s) {
+        for (int g = 0; g < GM_GROUPS; ++g) {
+            gm_mbar_init(aready0 + 8 * g, GM_DQ_WARPS);   // one arrival per dequant warp
+            gm_mbar_init(aempty0 + 8 * g, 1);             // tcgen05.commit after the group's MMAs
+        }
+        for (int s = 0; s < NW; ++s) {
             gm_mbar_init(wfull0 + 8 * s, 1);
             gm_mbar_init(wempty0 + 8 * s, GM_DQ_WARPS);   // every dequant warp has read its rows
         }
@@ -200,15 +253,16 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     }
     if (warp == 1) {
         // TMEM allocation by one full warp; the base address lands in shared memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gm_smem_u32(tmem_slot)), "r"(p.tmem_cols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(flags0), "r"(GM_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (warp >= 2 && warp < GM_WPRODUCER) {
-        // byte -> (bf16(code[hi]), bf16(code[lo])) table, one copy per lane (conflict-free lookups)
-        const float mine = __ldg(p.code16 + (lane & 15));
+        // byte -> (float(bf16(code[hi])), float(bf16(code[lo]))), one copy per lane (conflict-free lookups):
+        // entry e of lane l at window + e * 256 + l * 8
+        const float mine = __bfloat162float(__float2bfloat16_rn(__ldg(p.code16 + (lane & 15))));
         for (int e = warp - 2; e < 256; e += GM_DQ_WARPS) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(__shfl_sync(0xffffffffu, mine, e >> 4), __shfl_sync(0xffffffffu, mine, e & 15));
-            *reinterpret_cast<uint32_t*>(lut + e * 128 + lane * 4) = *reinterpret_cast<const uint32_t*>(&h);
+            const float first = __shfl_sync(0xffffffffu, mine, e >> 4), second = __shfl_sync(0xffffffffu, mine, e & 15);
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(GM_LUT_WINDOW + (uint32_t)(e * 256 + lane * 8)), "f"(first), "f"(second) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -223,145 +277,142 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         uint32_t parity = 0;
         if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");   // x comes from the upstream grid
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-            gm_wait(empty0 + 8 * slot, parity ^ 1u, abort_flag, 6, kb);
+            gm_wait(bempty0 + 8 * slot, parity ^ 1u, abort_flag, 6, kb);
             if (lane == 0) {
                 const uint32_t fb = full0 + 8 * slot;
                 gm_mbar_expect_tx(fb, (uint32_t)b_bytes);
-                gm_tma_2d(gm_smem_u32(b_base + slot * b_bytes), &p.xmap, kb * 64, m0, fb);
+                gm_tma_2d(p.b_addr[slot], &p.xmap, kb * 64, m0, fb);
             }
             __syncwarp();
-            if (++slot == GM_STAGES) { slot = 0; parity ^= 1u; }
+            if (++slot == NS) { slot = 0; parity ^= 1u; }
         }
     } else if (warp == GM_WPRODUCER) {
         // -------------------------------- weight producer --------------------------------------
-        // packed weights: one box of 128 rows x 128 bytes (GM_WKB K blocks) per weight stage, running up to
-        // GM_WSTAGES stages ahead of the dequant warps whatever the activation ring does; the weights do
+        // packed weights: one box of 128 rows x 128 bytes (a group of GM_WKB K blocks) per weight stage, running
+        // up to `wstages` groups ahead of the dequant warps whatever the activation ring does; the weights do
         // not depend on the upstream grid, so nothing here waits for it
         int wslot = 0;
         uint32_t wparity = 0;
         for (int kb = kb_begin; kb < kb_end; kb += GM_WKB) {
             gm_wait(wempty0 + 8 * wslot, wparity ^ 1u, abort_flag, 9, kb);
             if (lane == 0) {
-                gm_mbar_expect_tx(wfull0 + 8 * wslot, (uint32_t)GM_PK_BYTES);
-                gm_tma_2d(gm_smem_u32(pk_base + wslot * GM_PK_BYTES), &p.wmap, kb * 32, n0, wfull0 + 8 * wslot);
+                gm_mbar_expect_tx(wfull0 + 8 * wslot, (uint32_t)(GM_PK_BYTES + (p.am_tma ? GM_AM_BYTES : 0)));
+                gm_tma_2d(p.w_addr[wslot], &p.wmap, kb * 32, n0, wfull0 + 8 * wslot);
+                if (p.am_tma) gm_tma_2d(p.am_addr[wslot], &p.amap, kb, n0, wfull0 + 8 * wslot);
             }
             __syncwarp();
-            if (++wslot == GM_WSTAGES) { wslot = 0; wparity ^= 1u; }
+            if (++wslot == NW) { wslot = 0; wparity ^= 1u; }
         }
     } else if (warp == 1) {
         // ------------------------------------ MMA issuer ---------------------------------------
+        // per group of GM_WKB K blocks: one wait for the dequantised weights, 4 MMAs per K block as its
+        // activations land, one commit per K block (frees the activation stage) and one per group.
+        // This warp's instruction stream is serial and sits on the critical path of small tiles, so the
+        // descriptors are built once and the loop body is kept short.
         const uint32_t idesc = gm_instr_desc(TM);
-        int slot = 0;
-        uint32_t parity = 0;
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-            gm_wait(full0 + 8 * slot, parity, abort_flag, 5, kb);      // activations landed
-            gm_wait(aready0 + 8 * slot, parity, abort_flag, 7, kb);    // weights dequantised
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (lane == 0) {
-                const uint32_t a_tmem = tmem_d + (uint32_t)(TM + slot * GM_A_COLS);
-                const uint64_t bdesc = gm_smem_desc(gm_smem_u32(b_base + slot * b_bytes));
+        uint64_t bdesc_of[GM_MAX_STAGES];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t accumulate = (kb > kb_begin || k > 0) ? 1u : 0u;
+        for (int s = 0; s < GM_MAX_STAGES; ++s) bdesc_of[s] = gm_smem_desc(p.b_addr[s < NS ? s : 0]);
+        int slot = 0, g = 0;
+        uint32_t parity = 0, gparity = 0;
+        uint32_t accumulate = 0u;
+        for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GM_WKB) {
+            gm_wait(aready0 + 8 * g, gparity, abort_flag, 7, kb0);     // the group's weights are in TMEM
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int nblk = min(GM_WKB, kb_end - kb0);
+            uint32_t a_tmem = tmem_d + (uint32_t)(GM_A_COL0 + g * GM_WKB * GM_A_COLS);
+            for (int j = 0; j < nblk; ++j, a_tmem += GM_A_COLS) {
+                gm_wait(full0 + 8 * slot, parity, abort_flag, 5, kb0 + j);  // activations landed
+                if (lane == 0) {
+                    const uint64_t bdesc = slot == 0 ? bdesc_of[0] : slot == 1 ? bdesc_of[1] : slot == 2 ? bdesc_of[2] : bdesc_of[3];
                     // 16 K elements per instruction: 8 TMEM columns of the weights, 32 bytes (+2 in the
                     // descriptor's address field) inside the activations' swizzle atom
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\t"
-                        "setp.ne.u32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                        ::"r"(tmem_d), "r"(a_tmem + (uint32_t)(8 * k)), "l"(bdesc + (uint64_t)(2 * k)), "r"(idesc), "r"(accumulate)
-                        : "memory");
+                    gm_mma(tmem_d, a_tmem, bdesc, idesc, accumulate);
+                    gm_mma(tmem_d, a_tmem + 8u, bdesc + 2u, idesc, 1u);
+                    gm_mma(tmem_d, a_tmem + 16u, bdesc + 4u, idesc, 1u);
+                    gm_mma(tmem_d, a_tmem + 24u, bdesc + 6u, idesc, 1u);
+                    // frees the activation stage once these MMAs have read it
+                    gm_commit(bempty0 + 8 * slot);
                 }
-                // frees the stage once these MMAs have read it
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(empty0 + 8 * slot) : "memory");
-                if (kb == kb_end - 1)
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(accdone) : "memory");
+                accumulate = 1u;
+                if (++slot == NS) { slot = 0; parity ^= 1u; }
             }
-            __syncwarp();
-            if (++slot == GM_STAGES) { slot = 0; parity ^= 1u; }
+            if (lane == 0) gm_commit(aempty0 + 8 * g);     // the group's TMEM columns may be overwritten
+            if (++g == GM_GROUPS) { g = 0; gparity ^= 1u; }
         }
+        if (lane == 0) gm_commit(accdone);
+        __syncwarp();
     } else {
         // ------------------------------------ dequant warps -------------------------------------
         // a warp may touch only the TMEM lane quarter warp % 4, so rows follow that numbering
         const int q = warp & 3;
         const int r = q * 32 + lane;            // weight row inside the tile = TMEM lane
-        const int hsel = (warp - 2) >> 2;       // which half of the row's 64-block: bytes [16*hsel, 16*hsel+16)
+        const int part = (warp - 2) >> 2;       // which quarter of the row's 64-block: packed bytes [8*part, 8*part+8)
         const int grow = n0 + r;
-        const uint32_t lut_lane = gm_smem_u32(lut) + (uint32_t)lane * 4u;
+        const uint32_t window_lane = GM_LUT_WINDOW | (uint32_t)(lane << 3);
         const float* const am_row = p.absmax + (int64_t)(grow < p.N ? grow : 0) * p.KB;
-        const uint8_t* const pk_row = pk_base + r * 128;
-        const int rsw = r & 7;
-        int slot = 0;                            // TMEM weight stage (= activation stage) of the current K block
-        uint32_t parity = 0;
-        int wslot = 0;                           // packed stage the read-ahead is in
-        uint32_t wparity = 0;
-        int pending = -1;                        // TMEM stage written last, not yet announced
-        float am_next = grow < p.N ? __ldg(am_row + kb_begin) : 0.0f;
-        // The loop is software-pipelined over K blocks: the packed bytes of block kb+1 are read while block kb
-        // is converted, and the tcgen05.st of block kb is only waited for (and announced) after block kb+1
-        // has been converted, so neither latency sits on the chain.
-        gm_wait(wfull0, 0u, abort_flag, 5, kb_begin);
-        uint4 w_next = *reinterpret_cast<const uint4*>(pk_row + ((hsel ^ rsw) << 4));
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
-            const float am = am_next;
-            const uint4 w4 = w_next;
-            const int j = (kb - kb_begin) % GM_WKB;                     // K block inside the packed stage
-            const int rel_slot = wslot;                                 // packed stage of this K block
-            if (kb + 1 < kb_end) {
-                am_next = grow < p.N ? __ldg(am_row + kb + 1) : 0.0f;
-                int jn = j + 1;
-                if (jn == GM_WKB) {
-                    jn = 0;
-                    if (++wslot == GM_WSTAGES) { wslot = 0; wparity ^= 1u; }
-                    gm_wait(wfull0 + 8 * wslot, wparity, abort_flag, 5, kb + 1);   // next packed stage landed
+        const bool row_ok = grow < p.N;
+        // this thread's 8 bytes of K block j of a packed stage: 16-byte chunk 2j + part/2 at its swizzled place
+        const uint32_t pk_off = (uint32_t)(r * 128 + (part & 1) * 8);
+        const int rsw = r & 7, chunk0 = part >> 1;
+        const uint32_t tcol = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(GM_A_COL0 + part * 8);
+        int g = 0, wslot = 0;
+        uint32_t gparity = 0, wparity = 0;
+        // absmax of a group's K blocks is fetched one group ahead
+        float am_nxt[GM_WKB];
+#pragma unroll
+        for (int j = 0; j < GM_WKB; ++j) am_nxt[j] = (!p.am_tma && row_ok && kb_begin + j < kb_end) ? __ldg(am_row + kb_begin + j) : 0.0f;
+        for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GM_WKB) {
+            float am[GM_WKB];
+            if (!p.am_tma) {
+#pragma unroll
+                for (int j = 0; j < GM_WKB; ++j) {
+                    am[j] = am_nxt[j];
+                    am_nxt[j] = (row_ok && kb0 + GM_WKB + j < kb_end) ? __ldg(am_row + kb0 + GM_WKB + j) : 0.0f;
                 }
-                // 16 bytes of this row: logical 16-byte chunk 2j + hsel of the 128-byte row, at its swizzled place
-                w_next = *reinterpret_cast<const uint4*>(pk_row + wslot * GM_PK_BYTES + (((2 * jn + hsel) ^ rsw) << 4));
             }
-            const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
-            uint32_t pair[16];
+            gm_wait(wfull0 + 8 * wslot, wparity, abort_flag, 5, kb0);   // packed bytes (and absmax) landed
+            if (p.am_tma)
+                asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(am[0]), "=f"(am[1]), "=f"(am[2]), "=f"(am[3])
+                             : "r"(p.am_addr[wslot] + (uint32_t)(r * 16)));
+            uint2 w[GM_WKB];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {      // one word = 4 packed bytes = 8 weights; all 16 lookups in flight at once
-                const uint32_t byte = __byte_perm(words[i >> 2], 0u, 0x4440 | (i & 3));
-                asm("ld.shared.b32 %0, [%1];" : "=r"(pair[i]) : "r"(lut_lane + byte * 128u));
-            }
-            if (j == GM_WKB - 1 || kb == kb_end - 1) {
-                // this warp's last read of the packed stage has been consumed: hand the stage back
-                __syncwarp();
-                if (lane == 0) gm_mbar_arrive(wempty0 + 8 * rel_slot);
-            }
-            uint32_t out[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float lo = __uint_as_float(pair[i] << 16) * am;
-                const float hi = __uint_as_float(pair[i] & 0xffff0000u) * am;
-                const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                out[i] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-            if (pending >= 0) {
-                // the previous block's tcgen05.st has had a whole block's conversion to complete
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) gm_mbar_arrive(aready0 + 8 * pending);
-            }
-            gm_wait(empty0 + 8 * slot, parity ^ 1u, abort_flag, 6, kb); // the weight stage in TMEM is free
+            for (int j = 0; j < GM_WKB; ++j)
+                asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[j].x), "=r"(w[j].y)
+                             : "r"(p.w_addr[wslot] + pk_off + (uint32_t)(((2 * j + chunk0) ^ rsw) << 4)));
+            gm_wait(aempty0 + 8 * g, gparity ^ 1u, abort_flag, 6, kb0);  // this group's TMEM columns are free
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // 16 columns (32 consecutive K elements) of this thread's lane
-            const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(TM + slot * GM_A_COLS + hsel * 16);
-            asm volatile(
-                "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                ::"r"(taddr), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]), "r"(out[6]),
-                  "r"(out[7]), "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]), "r"(out[14]),
-                  "r"(out[15]) : "memory");
-            pending = slot;
-            if (++slot == GM_STAGES) { slot = 0; parity ^= 1u; }
-        }
-        if (pending >= 0) {
+#pragma unroll
+            for (int j = 0; j < GM_WKB; ++j) {
+                // 8 packed bytes -> 16 weights: all 8 lookups in flight, then scale and round.  Blocks past the
+                // end of the range convert whatever the box brought; no MMA reads them.
+                float f[16];
+                gm_lookup<0>(w[j].x, window_lane, f[0], f[1]);
+                gm_lookup<1>(w[j].x, window_lane, f[2], f[3]);
+                gm_lookup<2>(w[j].x, window_lane, f[4], f[5]);
+                gm_lookup<3>(w[j].x, window_lane, f[6], f[7]);
+                gm_lookup<0>(w[j].y, window_lane, f[8], f[9]);
+                gm_lookup<1>(w[j].y, window_lane, f[10], f[11]);
+                gm_lookup<2>(w[j].y, window_lane, f[12], f[13]);
+                gm_lookup<3>(w[j].y, window_lane, f[14], f[15]);
+                uint32_t out[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) out[i] = gm_scale_pack(f[2 * i], f[2 * i + 1], am[j]);
+                // 8 columns (16 consecutive K elements) of this thread's lane
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                                 ::"r"(tcol + (uint32_t)((g * GM_WKB + j) * GM_A_COLS)), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]),
+                                   "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+            }
+            // the packed stage has been consumed, the group is in TMEM: one hand-off each per 4 K blocks
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) gm_mbar_arrive(aready0 + 8 * pending);
+            if (lane == 0) {
+                gm_mbar_arrive(wempty0 + 8 * wslot);
+                gm_mbar_arrive(aready0 + 8 * g);
+            }
+            if (++wslot == NW) { wslot = 0; wparity ^= 1u; }
+            if (++g == GM_GROUPS) { g = 0; gparity ^= 1u; }
         }
         if (warp >= 6) goto done;               // the epilogue needs one warp per TMEM lane quarter
         // ------------------------------------ epilogue ------------------------------------------
@@ -371,6 +422,38 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         const int mlim = min(TM, p.M - m0);     // activation rows of this tile that exist
         const int group = mtile * gridDim.x + blockIdx.x;
         const uint32_t tacc = tmem_d + ((uint32_t)(q * 32) << 16);
+        __nv_bfloat16* const y = static_cast<__nv_bfloat16*>(p.y);
+        if (p.splits == 1 && p.epilogue == 0 && !p.residual && mlim > 16 && (p.N & 7) == 0 &&
+            (reinterpret_cast<uintptr_t>(p.y) & 15) == 0) {
+            // Tall tiles: round to bf16, transpose through shared memory (the activation stages are idle now:
+            // every MMA has completed), then store rows of y 16 bytes per lane.  Stage s holds rows
+            // [s * TM/2, (s+1) * TM/2) of the tile, 256 bytes (128 columns of y) each.
+            const float bias = (p.bias && gn < p.N) ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[gn]) : 0.0f;
+            const int half = TM >> 1;
+            for (int c0 = 0; c0 < mlim; c0 += 16) {
+                uint32_t v[16];
+                gm_tmem_ld16(tacc + (uint32_t)c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = c0 + j;
+                    const uint32_t dst = p.b_addr[m >= half ? 1 : 0] + (uint32_t)((m >= half ? m - half : m) * 256 + r * 2);
+                    const __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(v[j]) + bias);
+                    asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&h)) : "memory");
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int et = tid - 64;                      // 0..127 over the four epilogue warps
+            const int chunk = et & 15;                    // 16-byte chunk of a 256-byte row
+            const bool col_ok = n0 + chunk * 8 < p.N;
+            for (int m = et >> 4; m < mlim; m += 8) {
+                const uint32_t src = p.b_addr[m >= half ? 1 : 0] + (uint32_t)((m >= half ? m - half : m) * 256 + chunk * 16);
+                uint4 d;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "r"(src));
+                if (col_ok) *reinterpret_cast<uint4*>(y + (int64_t)(m0 + m) * p.N + n0 + chunk * 8) = d;
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            goto done;
+        }
         bool finish = true;
         if (p.splits > 1) {
             // every split parks its fp32 partial sums; the CTA that arrives last adds them in split order
@@ -397,7 +480,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         if (finish) {
             if (p.pdl && p.residual && p.splits == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
             const float bias = (p.bias && gn < p.N) ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[gn]) : 0.0f;
-            __nv_bfloat16* const y = static_cast<__nv_bfloat16*>(p.y);
             const __nv_bfloat16* const res = static_cast<const __nv_bfloat16*>(p.residual);
             for (int c0 = 0; c0 < mlim; c0 += 16) {
                 float v[16];
@@ -446,7 +528,7 @@ done:
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(p.tmem_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(GM_TMEM_COLS) : "memory");
     }
 }
 
@@ -470,26 +552,54 @@ static GmEncodeFn gm_encode_fn() {
     return fn;
 }
 
-static int gemm_smem_bytes(int TM) {
-    const int need = GM_STAGES * TM * 128 + GM_WSTAGES * GM_PK_BYTES + GM_LUT_BYTES + 256;
-    return need > GM_MIN_SMEM ? need : GM_MIN_SMEM;
+// Shared-memory map in shared-window addresses: the lookup table owns [64K, 128K); activation stages, packed
+// stages and the barriers are dealt, 1024-byte aligned, first into [GM_LOW_BASE, 64K), then from 128K up.
+// Returns the dynamic shared memory to request (the region starts at or below GM_LOW_BASE).
+static int gemm_layout(int TM, GemmParams* p) {
+    uint32_t low = GM_LOW_BASE, high = 2 * GM_LUT_WINDOW;
+    auto place = [&](uint32_t bytes) {
+        const uint32_t size = (bytes + 1023u) & ~1023u;
+        uint32_t addr;
+        if (low + size <= GM_LUT_WINDOW) { addr = low; low += size; }
+        else { addr = high; high += size; }
+        return addr;
+    };
+    const int stages = TM > 128 ? 3 : GM_MAX_STAGES, wstages = TM > 128 ? 3 : GM_MAX_WSTAGES;
+    if (p) { p->stages = stages; p->wstages = wstages; }
+    for (int s = 0; s < stages; ++s) {
+        const uint32_t a = place((uint32_t)TM * 128u);
+        if (p) p->b_addr[s] = a;
+    }
+    for (int s = 0; s < wstages; ++s) {
+        const uint32_t a = place((uint32_t)GM_PK_BYTES);
+        if (p) p->w_addr[s] = a;
+    }
+    for (int s = 0; s < wstages; ++s) {
+        const uint32_t a = place((uint32_t)GM_AM_BYTES);
+        if (p) p->am_addr[s] = a;
+    }
+    const uint32_t bars = place(256);
+    if (p) p->bar_addr = bars;
+    return (int)high;
 }
 
 constexpr int64_t GM_COUNTER_BYTES = 4096;   // head of the split-K workspace: arrival counters
 
 // Tile height and K split for a shape.  Few weight tiles (decode shapes, narrow layers) leave SMs idle, so K
-// is cut into ranges until about two small CTAs (or one large) per SM exist; each range keeps >= 4 K blocks.
+// is cut into ranges until about one CTA per SM exists; each range keeps >= 4 K blocks.
 static void gemm_plan(int64_t M, int64_t N, int64_t K, int* TM_out, int* splits_out) {
     int TM = 256;
     while (TM > 32 && TM / 2 >= M) TM /= 2;         // 32, 64, 128 or 256 activation rows per CTA
     const int64_t ctas = ((N + GM_BM - 1) / GM_BM) * ((M + TM - 1) / TM);
-    const int64_t target = TM <= 64 ? GM_MAX_CTAS_SPLIT : GM_MAX_CTAS_SPLIT / 2;
-    int64_t splits = target / ctas;
-    if (splits > K / 64 / 4) splits = K / 64 / 4;
+    int64_t splits = GM_SM_TARGET / ctas;            // one CTA per SM is resident
+    const int64_t KB = K / 64;
+    const int64_t max_splits = KB % GM_WKB == 0 ? KB / GM_WKB : KB;    // ranges are whole groups when they can be
+    if (splits > KB / 4) splits = KB / 4;
     if (splits < 1) splits = 1;
     const char* e = getenv("NF4_GEMM_SPLITS");
     const int forced = e ? atoi(e) : -1;
-    if (forced >= 1) splits = forced < K / 64 ? forced : K / 64;
+    if (forced >= 1) splits = forced;
+    if (splits > max_splits) splits = max_splits;
     *TM_out = TM;
     *splits_out = (int)splits;
 }
@@ -540,14 +650,25 @@ static int gemm_tcgen05(const void* x, int64_t M, int64_t K, const uint8_t* pack
         splits = 1;
     p.TM = TM;
     p.splits = splits;
-    p.tmem_cols = 32;                               // a power of two >= 32
-    while (p.tmem_cols < TM + GM_STAGES * GM_A_COLS) p.tmem_cols *= 2;
+    const int smem_bytes = gemm_layout(TM, &p);
     p.absmax = absmax; p.code16 = code16; p.bias = bias; p.y = y;
     p.residual = ex.residual; p.epilogue = ex.epilogue; p.pdl = ex.pdl;
     p.counters = static_cast<unsigned*>(ex.workspace);
     p.partials = ex.workspace ? reinterpret_cast<float*>(static_cast<uint8_t*>(ex.workspace) + GM_COUNTER_BYTES) : nullptr;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.KB = (int)(K / 64);
+    p.am_tma = (p.KB % GM_WKB == 0 && reinterpret_cast<uintptr_t>(absmax) % 16 == 0) ? 1 : 0;
     const cuuint32_t estr[2] = {1, 1};
+    if (p.am_tma) {
+        const cuuint64_t dim[2] = {(cuuint64_t)p.KB, (cuuint64_t)N};
+        const cuuint64_t str[1] = {(cuuint64_t)p.KB * 4};
+        const cuuint32_t box[2] = {(cuuint32_t)GM_WKB, (cuuint32_t)GM_BM};
+        CUresult r = enc(&p.amap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(absmax), dim, str, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        NF4_REQUIRE(r == CUDA_SUCCESS, NF4_ERR_CUDA, "gemm: cuTensorMapEncodeTiled(absmax) failed with %d", (int)r);
+    } else {
+        memset(&p.amap, 0, sizeof(p.amap));
+    }
     {
         const cuuint64_t dim[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
         const cuuint64_t str[1] = {(cuuint64_t)(K / 2)};
@@ -570,7 +691,7 @@ static int gemm_tcgen05(const void* x, int64_t M, int64_t K, const uint8_t* pack
     int dev = 0;
     NF4_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
-        NF4_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_smem_bytes(256)));
+        NF4_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
         configured[dev] = true;
     }
     dim3 grid((unsigned)ntiles, (unsigned)(mtiles * splits));
@@ -578,7 +699,7 @@ static int gemm_tcgen05(const void* x, int64_t M, int64_t K, const uint8_t* pack
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(GM_THREADS);
-    cfg.dynamicSmemBytes = (size_t)gemm_smem_bytes(TM);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

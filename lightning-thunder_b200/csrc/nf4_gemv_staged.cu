@@ -106,12 +106,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
-// Bounded wait.  Returns immediately once the CTA has given up (abort flag set).
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int stage) {
-    if (mbar_try_wait(bar, parity)) return;
+// Bounded wait.  The hot path is a plain poll of the barrier; only a wait that has already lasted thousands
+// of polls starts reading the timer and the CTA's abort flag (returns at once when the CTA has given up).
+__device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int stage) {
     if (*abort_flag) return;
     const unsigned long long t0 = global_ns();
-    while (!mbar_try_wait(bar, parity)) {
+    while (true) {
+        for (int spin = 0; spin < 256; ++spin)
+            if (mbar_try_wait(bar, parity)) return;
         if (*abort_flag) return;
         if (global_ns() - t0 > SG_WAIT_LIMIT_NS) {
             *abort_flag = 1;
@@ -123,6 +125,12 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
             return;
         }
     }
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, int stage) {
+#pragma unroll 1
+    for (int spin = 0; spin < 4096; ++spin)
+        if (mbar_try_wait(bar, parity)) return;
+    mbar_wait_slow(bar, parity, abort_flag, code, stage);
 }
 
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
