@@ -333,18 +333,40 @@ def run_decode(args):
     clocks = sampler.stop() if rank == 0 else None
     e2e_tok_s = steps * batch / e2e_s
 
-    # ---- roofline of the dominant kernel (the fused dequant-GEMV): one more decode step, not
-    # captured, with an event pair around every GEMV launch on the launching stream
+    # ---- roofline of the dominant kernel (the fused dequant-GEMV).  Algorithmic bytes of every GEMV launch
+    # of a step come from one uncaptured step (a hook records them); the duration comes from a CUDA graph
+    # holding exactly those launches (no glue kernels, no collectives), replayed and timed with events on
+    # the launching stream: cold weights and dependent back-to-back launches, as inside the step.
     dec.graph = None
     dec.gemv_events = ev = []
     dec.ids_in.copy_(dec.ids_out)
     dec.step()
     torch.cuda.synchronize()
     dec.gemv_events = None
-    gemv_us = [a.elapsed_time(b) * 1e3 for a, b, _ in ev]
     gemv_bytes = [n for _, _, n in ev]
+    for t in (dec.x, dec.attn, dec.h):
+        t.zero_()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        dec.linears_only()
+        side.synchronize()
+        chain = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(chain, stream=side, capture_error_mode="thread_local"):
+            dec.linears_only()
+        chain.replay()
+        side.synchronize()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, min(steps, 16))
+        c0.record(side)
+        for _ in range(reps):
+            chain.replay()
+        c1.record(side)
+        side.synchronize()
+    chain_us = c0.elapsed_time(c1) * 1e3 / reps
+    gemv_us = [chain_us / len(ev)] * len(ev)
     peaks, src = measured_peaks()
-    achieved = sum(gemv_bytes) / sum(gemv_us) / 1e3       # GB/s over all GEMV launches of a step
+    achieved = sum(gemv_bytes) / chain_us / 1e3           # GB/s over all GEMV launches of a step
     dev_err = _lib.device_error()
 
     def finish():

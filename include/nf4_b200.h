@@ -71,10 +71,10 @@ int nf4_b200_dequantize(const uint8_t* packed, const float* absmax, const float*
  *               (may be NULL when that is 0).  It must be zero-filled once before its first use; every
  *               call leaves it ready for the next one.  One workspace serves one stream at a time.
  *               Without it the result is the same sums computed by fewer thread blocks.
- * Dispatch: M <= 8 with K % 64 == 0, blocksize 64 and 16-bit dtype -> fused dequant-GEMV
+ * Dispatch: M <= 16 with K % 64 == 0, blocksize 64 and 16-bit dtype -> fused dequant-GEMV
  * (weights streamed once); larger M (bf16) -> tensor-core dequant-GEMM, K split over thread blocks when
- * the weight has few 128-row tiles; fp16 up to M = 16 -> GEMV; anything else (fp32, ragged K, other
- * blocksizes) -> a generic kernel.  fp32 accumulation everywhere.
+ * the weight has few 128-row tiles; anything else (fp32, ragged K, other blocksizes) -> a generic
+ * kernel.  fp32 accumulation everywhere.
  */
 int nf4_b200_linear(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
                     const float* code16, int64_t N, int blocksize, const void* bias, void* y, int dtype,
@@ -98,7 +98,7 @@ int64_t nf4_b200_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
  * The tensor-core kernel with a decode step's epilogues (bf16 only): y = x . dequant(W)^T + residual
  * (epilogue 0; residual [M,N] may be NULL or alias y), or, with weight rows stored as (gate_i, up_i)
  * pairs, y[M, N/2] = silu(gate) * up (epilogue 1; both sums rounded to bf16 first).  The batched
- * counterpart of nf4_b200_gemv_decode for more than 8 sequences; no counterpart in the reference.
+ * counterpart of nf4_b200_gemv_decode for batches beyond the GEMV's 16 rows; no counterpart in the reference.
  * workspace as for nf4_b200_linear (nf4_b200_gemm_workspace_bytes); flags bit 0: programmatic dependent
  * launch (the weights of the first K blocks are fetched while the upstream kernel drains).
  */

@@ -53,12 +53,13 @@ constexpr int GM_DQ_WARPS = 16;          // dequant warps: four threads per weig
 constexpr int GM_THREADS = (3 + GM_DQ_WARPS) * 32;   // activation producer, MMA, dequant (the first 4 also run the epilogue), weight producer
 constexpr int GM_WPRODUCER = 2 + GM_DQ_WARPS;        // warp index of the weight producer
 constexpr int GM_BM = 128;               // weight rows per CTA (UMMA M)
-constexpr int GM_MAX_STAGES = 4;         // activation stages (= weight stages in TMEM): 4, or 3 for 256-row tiles
+constexpr int GM_MAX_STAGES = 8;         // activation stages: 8 (tiles up to 64 rows), 4 (128 rows) or 3 (256 rows)
+constexpr int GM_DONE = 8;               // ring of "MMAs up to here have completed" barriers, one per release unit
 constexpr int GM_A_COLS = 32;            // TMEM columns of one K block of weights: 64 bf16 per row, two per column
 constexpr int GM_GROUPS = 2;             // weight groups (GM_WKB K blocks each) in TMEM: one converts while one multiplies
 constexpr int GM_A_COL0 = 256;           // accumulator in TMEM columns [0, 256), weight groups in [256, 512)
 constexpr int GM_TMEM_COLS = 512;
-constexpr int GM_MAX_WSTAGES = 5;        // packed-weight stages, each GM_WKB K blocks deep: 5, or 3 for 256-row tiles
+constexpr int GM_MAX_WSTAGES = 4;        // packed-weight stages, each GM_WKB K blocks deep: 4, or 3 for 256-row tiles
 constexpr int GM_WKB = 4;                // K blocks per packed-weight stage: 4 x 32 B = one 128-byte swizzle row
 constexpr int GM_PK_BYTES = GM_BM * 128; // one packed-weight stage
 constexpr int GM_AM_BYTES = GM_BM * 16;  // its absmax: 4 floats per row
@@ -84,6 +85,9 @@ struct alignas(64) GemmParams {
     int epilogue;         // 0: y[m][n];  1: rows are (gate, up) pairs, y[m][n/2] = silu(gate) * up
     int pdl;              // programmatic dependent launch: weights may be fetched before the upstream grid ends
     int stages, wstages;  // ring depths
+    int ru_shift;         // log2 of the K blocks per release unit: the MMA thread commits once per unit (a commit stalls it
+                          // for about as long as two MMAs), which frees the unit's activation stages and tells
+                          // the dequant warps how far the tensor core has got
     // shared-window addresses (the table takes [64K, 128K); the host lays the rest out around it)
     uint32_t b_addr[GM_MAX_STAGES];    // activation stages, 1024-byte aligned
     uint32_t w_addr[GM_MAX_WSTAGES];   // packed-weight stages, 1024-byte aligned
@@ -217,9 +221,11 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         if (tid == 0 && atomicCAS(&g_gemm_error[0], 0u, 10u) == 0u) g_gemm_error[1] = s0;
         return;
     }
-    const uint32_t full0 = p.bar_addr, bempty0 = full0 + 8 * GM_MAX_STAGES, aready0 = bempty0 + 8 * GM_MAX_STAGES,
-                   aempty0 = aready0 + 8 * GM_GROUPS, accdone = aempty0 + 8 * GM_GROUPS, wfull0 = accdone + 8,
+    const uint32_t full0 = p.bar_addr, done0 = full0 + 8 * GM_MAX_STAGES, aready0 = done0 + 8 * GM_DONE,
+                   accdone = aready0 + 8 * GM_GROUPS, wfull0 = accdone + 8,
                    wempty0 = wfull0 + 8 * GM_MAX_WSTAGES, flags0 = wempty0 + 8 * GM_MAX_WSTAGES;
+    const uint32_t desc0 = flags0 + 16;              // activation descriptors per stage (8 x 8 bytes)
+    const int ru_shift = p.ru_shift, ru_mask = (1 << ru_shift) - 1;
     uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + (flags0 - s0));
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* const last_flag = abort_flag + 1;
@@ -235,20 +241,19 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     const int kb_end = (int)((int64_t)units * (split + 1) / p.splits) * unit;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) {
-            gm_mbar_init(full0 + 8 * s, 1);
-            gm_mbar_init(bempty0 + 8 * s, 1);             // tcgen05.commit after the K block's MMAs
-        }
-        for (int g = 0; g < GM_GROUPS; ++g) {
-            gm_mbar_init(aready0 + 8 * g, GM_DQ_WARPS);   // one arrival per dequant warp
-            gm_mbar_init(aempty0 + 8 * g, 1);             // tcgen05.commit after the group's MMAs
-        }
+        for (int s = 0; s < NS; ++s) gm_mbar_init(full0 + 8 * s, 1);
+        for (int s = 0; s < GM_DONE; ++s) gm_mbar_init(done0 + 8 * s, 1);   // tcgen05.commit after a unit's MMAs
+        for (int g = 0; g < GM_GROUPS; ++g) gm_mbar_init(aready0 + 8 * g, GM_DQ_WARPS);   // one arrival per dequant warp
         for (int s = 0; s < NW; ++s) {
             gm_mbar_init(wfull0 + 8 * s, 1);
             gm_mbar_init(wempty0 + 8 * s, GM_DQ_WARPS);   // every dequant warp has read its rows
         }
         gm_mbar_init(accdone, 1);
         *abort_flag = 0;
+        for (int s = 0; s < NS; ++s) {
+            const uint64_t d = gm_smem_desc(p.b_addr[s]);
+            asm volatile("st.shared.b64 [%0], %1;" ::"r"(desc0 + 8 * s), "l"(d) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -274,17 +279,20 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     if (warp == 0) {
         // ------------------------------ activation producer -----------------------------------
         int slot = 0;
-        uint32_t parity = 0;
         if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");   // x comes from the upstream grid
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-            gm_wait(bempty0 + 8 * slot, parity ^ 1u, abort_flag, 6, kb);
+            const int i = kb - kb_begin;
+            if (i >= NS) {      // the stage's previous K block belongs to unit u: wait until that unit's MMAs are done
+                const int u = (i - NS) >> ru_shift;
+                gm_wait(done0 + 8 * (u % GM_DONE), (uint32_t)((u / GM_DONE) & 1), abort_flag, 6, kb);
+            }
             if (lane == 0) {
                 const uint32_t fb = full0 + 8 * slot;
                 gm_mbar_expect_tx(fb, (uint32_t)b_bytes);
                 gm_tma_2d(p.b_addr[slot], &p.xmap, kb * 64, m0, fb);
             }
             __syncwarp();
-            if (++slot == NS) { slot = 0; parity ^= 1u; }
+            if (++slot == NS) slot = 0;
         }
     } else if (warp == GM_WPRODUCER) {
         // -------------------------------- weight producer --------------------------------------
@@ -310,34 +318,32 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         // This warp's instruction stream is serial and sits on the critical path of small tiles, so the
         // descriptors are built once and the loop body is kept short.
         const uint32_t idesc = gm_instr_desc(TM);
-        uint64_t bdesc_of[GM_MAX_STAGES];
-#pragma unroll
-        for (int s = 0; s < GM_MAX_STAGES; ++s) bdesc_of[s] = gm_smem_desc(p.b_addr[s < NS ? s : 0]);
-        int slot = 0, g = 0;
+        int slot = 0, g = 0, i = 0;              // i: K block index inside this CTA's range
         uint32_t parity = 0, gparity = 0;
         uint32_t accumulate = 0u;
+        const int nkb = kb_end - kb_begin;
         for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GM_WKB) {
             gm_wait(aready0 + 8 * g, gparity, abort_flag, 7, kb0);     // the group's weights are in TMEM
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int nblk = min(GM_WKB, kb_end - kb0);
             uint32_t a_tmem = tmem_d + (uint32_t)(GM_A_COL0 + g * GM_WKB * GM_A_COLS);
-            for (int j = 0; j < nblk; ++j, a_tmem += GM_A_COLS) {
+            for (int j = 0; j < nblk; ++j, a_tmem += GM_A_COLS, ++i) {
                 gm_wait(full0 + 8 * slot, parity, abort_flag, 5, kb0 + j);  // activations landed
                 if (lane == 0) {
-                    const uint64_t bdesc = slot == 0 ? bdesc_of[0] : slot == 1 ? bdesc_of[1] : slot == 2 ? bdesc_of[2] : bdesc_of[3];
+                    uint64_t bdesc;
+                    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(bdesc) : "r"(desc0 + 8 * slot));
                     // 16 K elements per instruction: 8 TMEM columns of the weights, 32 bytes (+2 in the
                     // descriptor's address field) inside the activations' swizzle atom
                     gm_mma(tmem_d, a_tmem, bdesc, idesc, accumulate);
                     gm_mma(tmem_d, a_tmem + 8u, bdesc + 2u, idesc, 1u);
                     gm_mma(tmem_d, a_tmem + 16u, bdesc + 4u, idesc, 1u);
                     gm_mma(tmem_d, a_tmem + 24u, bdesc + 6u, idesc, 1u);
-                    // frees the activation stage once these MMAs have read it
-                    gm_commit(bempty0 + 8 * slot);
+                    // one commit per release unit (and at the end of the range)
+                    if (((i + 1) & ru_mask) == 0 || i == nkb - 1) gm_commit(done0 + 8 * ((i >> ru_shift) & (GM_DONE - 1)));
                 }
                 accumulate = 1u;
                 if (++slot == NS) { slot = 0; parity ^= 1u; }
             }
-            if (lane == 0) gm_commit(aempty0 + 8 * g);     // the group's TMEM columns may be overwritten
             if (++g == GM_GROUPS) { g = 0; gparity ^= 1u; }
         }
         if (lane == 0) gm_commit(accdone);
@@ -371,6 +377,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
                     am_nxt[j] = (row_ok && kb0 + GM_WKB + j < kb_end) ? __ldg(am_row + kb0 + GM_WKB + j) : 0.0f;
                 }
             }
+            const int gi = (kb0 - kb_begin) / GM_WKB;
             gm_wait(wfull0 + 8 * wslot, wparity, abort_flag, 5, kb0);   // packed bytes (and absmax) landed
             if (p.am_tma)
                 asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(am[0]), "=f"(am[1]), "=f"(am[2]), "=f"(am[3])
@@ -380,7 +387,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
             for (int j = 0; j < GM_WKB; ++j)
                 asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[j].x), "=r"(w[j].y)
                              : "r"(p.w_addr[wslot] + pk_off + (uint32_t)(((2 * j + chunk0) ^ rsw) << 4)));
-            gm_wait(aempty0 + 8 * g, gparity ^ 1u, abort_flag, 6, kb0);  // this group's TMEM columns are free
+            if (gi >= GM_GROUPS) {   // these TMEM columns held group gi-2: its last K block's unit must be done
+                const int u = ((gi - GM_GROUPS) * GM_WKB + GM_WKB - 1) >> ru_shift;
+                gm_wait(done0 + 8 * (u % GM_DONE), (uint32_t)((u / GM_DONE) & 1), abort_flag, 6, kb0);
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int j = 0; j < GM_WKB; ++j) {
@@ -564,8 +574,11 @@ static int gemm_layout(int TM, GemmParams* p) {
         else { addr = high; high += size; }
         return addr;
     };
-    const int stages = TM > 128 ? 3 : GM_MAX_STAGES, wstages = TM > 128 ? 3 : GM_MAX_WSTAGES;
-    if (p) { p->stages = stages; p->wstages = wstages; }
+    // activation ring and release unit: 8 stages freed 4 at a time for small tiles, 4 freed in pairs for
+    // 128-row tiles, 3 freed one by one for 256-row tiles (all that fits beside the table)
+    const int stages = TM > 128 ? 3 : TM > 64 ? 4 : 8, ru = TM > 128 ? 1 : TM > 64 ? 2 : 4;
+    const int wstages = TM > 128 ? 3 : GM_MAX_WSTAGES;
+    if (p) { p->stages = stages; p->wstages = wstages; p->ru_shift = ru == 4 ? 2 : ru == 2 ? 1 : 0; }
     for (int s = 0; s < stages; ++s) {
         const uint32_t a = place((uint32_t)TM * 128u);
         if (p) p->b_addr[s] = a;
@@ -578,7 +591,7 @@ static int gemm_layout(int TM, GemmParams* p) {
         const uint32_t a = place((uint32_t)GM_AM_BYTES);
         if (p) p->am_addr[s] = a;
     }
-    const uint32_t bars = place(256);
+    const uint32_t bars = place(512);
     if (p) p->bar_addr = bars;
     return (int)high;
 }
@@ -616,7 +629,7 @@ static int64_t gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 // smallest M the dispatcher sends to this kernel instead of the GEMV (NF4_GEMM_MIN_M overrides)
 int gemm_min_m() {
     const char* e = getenv("NF4_GEMM_MIN_M");
-    const int v = e ? atoi(e) : 9;
+    const int v = e ? atoi(e) : 17;     // up to 16 rows the fused GEMV is faster on every shape measured
     return v < 1 ? 1 : v;
 }
 

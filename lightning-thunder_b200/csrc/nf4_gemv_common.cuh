@@ -71,10 +71,13 @@ __device__ __forceinline__ uint32_t lut_lookup(uint32_t w, uint32_t window_lane)
 
 // Fills the table: entry e (a packed byte) -> levels of its high and low nibble, one copy per lane.
 // Called by `nwarps` warps (warp index `warp`); lut_ptr is the generic address of the window.
-template <typename T>
-__device__ __forceinline__ void lut_build(uint8_t* lut_ptr, const float* __restrict__ code16, int warp, int nwarps, int lane) {
-    for (int e = warp; e < 256; e += nwarps) {
-        const uint32_t v = Mma<T>::pack(__ldg(code16 + (e >> 4)), __ldg(code16 + (e & 15)));
+// `level` is code16[lane & 15], loaded by the caller as early as it can (one global latency, not 32).
+template <typename T, int NWARPS>
+__device__ __forceinline__ void lut_build(uint8_t* lut_ptr, float level, int warp, int lane) {
+#pragma unroll
+    for (int i = 0; i < 256 / NWARPS; ++i) {      // independent iterations: the shuffles and stores pipeline
+        const int e = warp + i * NWARPS;
+        const uint32_t v = Mma<T>::pack(__shfl_sync(0xffffffffu, level, e >> 4), __shfl_sync(0xffffffffu, level, e & 15));
         *reinterpret_cast<uint32_t*>(lut_ptr + e * 256 + lane * 4) = v;
     }
 }

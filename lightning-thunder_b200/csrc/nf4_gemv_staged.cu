@@ -61,6 +61,7 @@ struct alignas(64) StagedParams {
     int epilogue;    // 0: y[m][n]; 1: rows come in (gate, up) pairs and y[m][n/2] = silu(gate) * up
     // offsets from the start of dynamic shared memory
     int off_bars, off_part, off_x;
+    int h_base, h_rem;   // halves of 8 rows per CTA: h_base, plus one for the first h_rem CTAs
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -235,9 +236,9 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
 
     // rows are dealt out in halves of 8: a CTA owns [8*h0, 8*h1); full 16-row tiles first, then at
     // most one half tile
-    const int H = (p.N + 7) >> 3;
-    const int h0 = (int)(((int64_t)H * blockIdx.x) / gridDim.x);
-    const int h1 = (int)(((int64_t)H * (blockIdx.x + 1)) / gridDim.x);
+    const int bid = (int)blockIdx.x;
+    const int h0 = bid * p.h_base + min(bid, p.h_rem);
+    const int h1 = h0 + p.h_base + (bid < p.h_rem ? 1 : 0);
     const int r0 = h0 * 8;
     const int r1 = min(h1 * 8, p.N);
     const int nhalves = h1 - h0;
@@ -248,17 +249,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
         if (tid == 0 && atomicCAS(&g_gemv_error[0], 0u, 4u) == 0u) g_gemv_error[1] = blockIdx.x;
         return;
     }
-    if (tid == 0) {
-        for (int s = 0; s < p.NS; ++s) {
-            mbar_init(full0 + s * 8, 1);
-            mbar_init(empty0 + s * 8, CW);
-        }
-        mbar_init(xbar, 1);
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    griddep_launch();
+    // The start of the kernel is a chain of latencies (first weight boxes, the level table's source, the
+    // activations), so they are all put in flight before anybody waits: the producer's first lane arms
+    // the barriers, signals that (a non-blocking arrival at named barrier 2) and starts issuing boxes;
+    // the compute warps fetch the levels, build the table and start the activation copy meanwhile and
+    // then wait on barrier 2, which makes the armed barriers and the table visible to all of them.
+    const float level = warp < CW ? __ldg(p.code16 + (lane & 15)) : 0.0f;
 
     // Both roles walk the same schedule: groups of up to TG full tiles, then the half tile alone;
     // inside a group: for every K segment, every tile of the group -> one stage each.
@@ -266,6 +262,17 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
         // ------------------------------- producer warp --------------------------------------
         // The weights do not depend on the previous kernel, so this warp never waits for it; the
         // activations are fetched by compute warp 0 once the predecessor grid has finished.
+        if (lane == 0) {
+            for (int s = 0; s < p.NS; ++s) {
+                mbar_init(full0 + s * 8, 1);
+                mbar_init(empty0 + s * 8, CW);
+            }
+            *abort_flag = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
+        griddep_launch();
         int stage = 0, slot = 0;
         uint32_t parity = 0;
         for (int tile0 = 0; tile0 < ntiles;) {
@@ -273,7 +280,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             const int nt_here = half ? 1 : min(TG, nfull - tile0);
             for (int seg = 0; seg < p.nseg; ++seg) {
                 for (int j = 0; j < nt_here; ++j) {
-                    mbar_wait(empty0 + slot * 8, parity ^ 1u, abort_flag, 2, stage);
+                    if (stage >= p.NS) mbar_wait(empty0 + slot * 8, parity ^ 1u, abort_flag, 2, stage);
                     if (lane == 0) {
                         const int row0 = r0 + (tile0 + j) * 16;
                         const uint32_t fullb = full0 + slot * 8;
@@ -293,9 +300,25 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     }
 
     // ----------------------------------- compute warps ------------------------------------------
-    lut_build<T>(lut_ptr, p.code16, warp, CW, lane);
-    // the table is complete for everybody after this barrier (compute warps only)
-    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    if (p.x_staged && warp == 0) {
+        // the activations come from the predecessor grid: wait for it here, start the copy, and let the
+        // table build below hide its latency
+        if (lane == 0) {
+            mbar_init(xbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        griddep_wait();
+        const uint32_t x_row_bytes = (uint32_t)(p.K * 2) * (p.prologue == 2 ? 2u : 1u);
+        if (lane == 0) mbar_expect_tx(xbar, (uint32_t)p.M * x_row_bytes);
+        __syncwarp();
+        if (lane < p.M)
+            bulk_g2s(xs_u32 + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * x_row_bytes,
+                     x_row_bytes, xbar);
+    }
+    lut_build<T, CW>(lut_ptr, level, warp, lane);
+    // barriers armed (producer) and table complete (compute warps) for every compute warp after this
+    asm volatile("bar.sync 2, %0;" ::"n"((CW + 1) * 32) : "memory");
+    griddep_launch();
     // RMSNorm weights are parameters, not activations: fetch them before waiting for the predecessor
     constexpr int NTH = CW * 32;
     constexpr int NWC = 8;                          // pairs per thread held in registers (K <= 16 * NTH)
@@ -310,17 +333,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
         }
     }
     griddep_wait();
-    if (p.x_staged) {
-        if (warp == 0) {
-            const uint32_t x_row_bytes = (uint32_t)(p.K * 2) * (p.prologue == 2 ? 2u : 1u);
-            if (lane == 0) mbar_expect_tx(xbar, (uint32_t)p.M * x_row_bytes);
-            __syncwarp();
-            if (lane < p.M)
-                bulk_g2s(xs_u32 + lane * p.x_stride, static_cast<const uint8_t*>(p.x) + (int64_t)lane * x_row_bytes,
-                         x_row_bytes, xbar);
-        }
-        mbar_wait(xbar, 0u, abort_flag, 3, -1);
-    }
+    if (p.x_staged) mbar_wait(xbar, 0u, abort_flag, 3, -1);
 
     // ---- optional prologue on the staged activations (in place, every CTA for itself) ----------
     if (p.prologue != 0) {
@@ -692,6 +705,8 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     StagedParams p;
     p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.residual = residual; p.y = y;
     p.M = M; p.N = N; p.K = K; p.KB = KB; p.SB = SB; p.nseg = KB / SB;
+    p.h_base = H / grid;
+    p.h_rem = H % grid;
     p.RS = SB * 32 + 32;
     p.AS = SB * 4 + 16;
     p.stage_bytes = 16 * p.RS + 16 * p.AS;

@@ -72,7 +72,7 @@ def _seeded_normal(shape, seed: int, device, std=0.02) -> torch.Tensor:
 class NF4Decoder:
     def __init__(self, cfg: DecoderConfig, batch: int, max_seq: int, device="cuda:0", seed: int = 0, tp_rank: int = 0,
                  tp_size: int = 1, group=None, attn_splits: int | None = None, fused: bool = True, pdl: bool = True,
-                 tensor_core_from: int = 9):
+                 tensor_core_from: int = 17):
         assert cfg.head_dim == 128, "the attention kernel is written for head_dim 128"
         assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.ffn % (64 * tp_size) == 0
         assert cfg.vocab % tp_size == 0 and batch <= 16
@@ -90,7 +90,8 @@ class NF4Decoder:
         self.fused = fused
         self.flags = 1 if (fused and pdl) else 0
         # from this many sequences on, the fused step's linears run on the tensor-core kernel (K split over
-        # thread blocks, residual / SwiGLU epilogues) with RMSNorm as a separate small kernel before it
+        # thread blocks, residual / SwiGLU epilogues) with RMSNorm as a separate small kernel before it;
+        # up to 16 sequences the GEMV measures faster on every layer shape, so that is the default
         self.tensor_core = fused and batch >= tensor_core_from
         self.Hq = cfg.n_heads // tp_size
         self.Hkv = cfg.n_kv_heads // tp_size
@@ -279,6 +280,20 @@ class NF4Decoder:
         ck(lib.nf4_b200_argmax(self.logits.data_ptr(), self.ids_out.data_ptr(), B, self.V, st), "argmax")
         self._n += 1
         self._finish_step()
+
+    def linears_only(self) -> None:
+        """Launches only the quantized linears of one fused decode step (same shapes, prologues, epilogues and
+        launch flags, no glue kernels, no collectives): the benchmark captures this chain in a CUDA graph to
+        time the GEMV by itself under the step's own conditions (cold weights, back-to-back dependent launches)."""
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
+        self._n = 0
+        tp = self.tp_size > 1
+        for layer in self.layers:
+            self._linear_decode(self.x, layer["qkv"], self.qkv, prologue=1, norm_w=layer["norm1"], stream=st)
+            self._linear_decode(self.attn, layer["o"], self.part if tp else self.x, residual=self.x, stream=st)
+            self._linear_decode(self.x, layer["gu"], self.h, prologue=1, norm_w=layer["norm2"], swiglu=True, stream=st)
+            self._linear_decode(self.h, layer["down"], self.part if tp else self.x, residual=self.x, stream=st)
+        self._linear_decode(self.x, self.lm_head, self.logits, prologue=1, norm_w=self.final_norm, stream=st)
 
     def _finish_step(self) -> None:
         if self.tp_size > 1:

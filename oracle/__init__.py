@@ -103,9 +103,9 @@ REF_DEQUANT_MATMUL_MODE, GEMV_MODE, GEMM_MODE = 0, 1, 2
 
 
 def linear_mode_for(M: int) -> int:
-    """The regime the library takes for M bf16 activation rows (fused GEMV up to 8 rows, tensor-core
+    """The regime the library takes for M bf16 activation rows (fused GEMV up to 16 rows, tensor-core
     GEMM above)."""
-    return GEMV_MODE if M <= 8 else GEMM_MODE
+    return GEMV_MODE if M <= 16 else GEMM_MODE
 
 
 def linear_bf16(x_bits: np.ndarray, packed, absmax, code16, N: int, K: int, blocksize: int = 64, bias_bits=None,

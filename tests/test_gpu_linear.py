@@ -16,8 +16,8 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 RTOL, ATOL = 1.6e-2, 1e-2
 
 
-# M > 8 in bf16 runs the tcgen05 GEMM (weights = the GEMV's weights rounded to bf16); fp16 runs
-# the GEMV kernel once per slab of 16 activation rows.  NF4_GEMM_MIN_M=17 keeps M = 9..16 on the GEMV.
+# M > 16 in bf16 runs the tcgen05 GEMM (weights = the GEMV's weights rounded to bf16); fp16 runs
+# the GEMV kernel once per slab of 16 activation rows.  NF4_GEMM_MIN_M=9 sends M = 9..16 to the GEMM too.
 GEMM_ORACLE_MODE = oracle.GEMM_MODE
 
 
@@ -74,10 +74,9 @@ def test_gemv_every_plan(nf4_code_np, plan, monkeypatch):
     """Forces each (rows-per-warp, K-split) variant of the GEMV on the same problem."""
     monkeypatch.setenv("NF4_GEMV_KERNEL", "direct")
     monkeypatch.setenv("NF4_GEMV_PLAN", plan)
-    monkeypatch.setenv("NF4_GEMM_MIN_M", "17")
     w = seeded_weight((1500, 2048), 17)
     for M in (1, 5, 12):
-        _check(seeded_act((M, 2048), M + 100), w, nf4_code_np, mode=oracle.GEMV_MODE)
+        _check(seeded_act((M, 2048), M + 100), w, nf4_code_np)
 
 
 @pytest.mark.parametrize("kernel", ["direct", "staged"])
@@ -89,9 +88,8 @@ def test_gemv_both_kernels(nf4_code_np, kernel, M, N, K, monkeypatch):
     from nf4_b200 import _lib
 
     monkeypatch.setenv("NF4_GEMV_KERNEL", kernel)
-    monkeypatch.setenv("NF4_GEMM_MIN_M", "17")
     w = seeded_weight((N, K), N + 3 * K)
-    _check(seeded_act((M, K), M), w, nf4_code_np, bias_cpu=seeded_act((N,), 2), mode=oracle.GEMV_MODE)
+    _check(seeded_act((M, K), M), w, nf4_code_np, bias_cpu=seeded_act((N,), 2))
     assert _lib.device_error()[0] == 0
 
 
@@ -101,10 +99,9 @@ def test_gemv_staged_group_sizes(nf4_code_np, tg, monkeypatch):
 
     monkeypatch.setenv("NF4_GEMV_KERNEL", "staged")
     monkeypatch.setenv("NF4_GEMV_TG", tg)
-    monkeypatch.setenv("NF4_GEMM_MIN_M", "17")
     w = seeded_weight((128256 // 8, 4096), 5)     # 108 rows per CTA: several groups, ragged last tile
     for M in (1, 6, 16):
-        _check(seeded_act((M, 4096), M + 50), w, nf4_code_np, mode=oracle.GEMV_MODE)
+        _check(seeded_act((M, 4096), M + 50), w, nf4_code_np)
     assert _lib.device_error()[0] == 0
 
 
@@ -222,10 +219,11 @@ def test_gemm_split_k(nf4_code_np, splits, M, N, K, monkeypatch):
     from nf4_b200 import _lib
 
     monkeypatch.setenv("NF4_GEMM_SPLITS", splits)
+    monkeypatch.setenv("NF4_GEMM_MIN_M", "9")
     w = seeded_weight((N, K), N + K + 1)
     x = seeded_act((M, K), M + 2)
-    y1 = _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9))
-    y2 = _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9))
+    y1 = _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9), mode=oracle.GEMM_MODE)
+    y2 = _check(x, w, nf4_code_np, bias_cpu=seeded_act((N,), 9), mode=oracle.GEMM_MODE)
     assert torch.equal(y1, y2)
     assert _lib.device_error()[0] == 0
 
@@ -236,6 +234,7 @@ def test_gemm_planned_split_matches_unsplit(nf4_code_np, monkeypatch):
     import nf4_b200
     from nf4_b200 import _lib
 
+    monkeypatch.setenv("NF4_GEMM_MIN_M", "9")
     lib = _lib.load()
     M, N, K = 16, 4096, 4096
     assert lib.nf4_b200_gemm_workspace_bytes(M, N, K) > 0          # 32 weight tiles: a split is planned
