@@ -81,7 +81,15 @@ class ClockSampler:
 # reference arm / CPU baseline: the oracle's linears on the host cores
 # --------------------------------------------------------------------------------------------
 
-def cpu_decode_sample(cfg_name: str, batch: int, reps: int):
+def workload_config(name: str, batch: int, prompt_len: int, world: int, step_bytes: float) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": f"{name} NF4 decode, batch {batch}, {prompt_len}-token prompt in the KV cache, greedy",
+            "parallelism": f"tp{world}", "global_batch": batch, "context": prompt_len,
+            "l2": f"{step_bytes / 1e9:.2f} GB of weights stream per step per GPU (> L2), no flush needed",
+            "blocksize": 64, "double_quant": False}
+
+
+def cpu_decode_sample(cfg_name: str, batch: int, reps: int, warmup: int = 0):
     """Times the quantized linears of ONE decoder layer (QKV, attention output, gate+up, down) at
     `batch` activation rows with the CPU oracle (OpenMP, all host threads), `reps` times, and scales
     to a whole model: tok/s = batch / (n_layers * t_layer + t_head_estimate).  Weights come from the
@@ -104,11 +112,12 @@ def cpu_decode_sample(cfg_name: str, batch: int, reps: int):
         x = oracle.f32_to_bf16_bits(rng.standard_normal((batch, K), dtype=np.float32))
         mats.append((x, packed, absmax, N, K))
     times = []
-    for _ in range(reps):
+    for it in range(warmup + reps):
         t0 = time.perf_counter()
         for (x, packed, absmax, N, K) in mats:
             oracle.linear_bf16(x, packed, absmax, code, N, K, 64, mode=oracle.GEMV_MODE)
-        times.append(time.perf_counter() - t0)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
     t_layer = statistics.median(times)
     layer_weights = sum(N * K for (_, _, _, N, K) in mats)
     t_head = t_layer * (cfg.vocab * D) / layer_weights
@@ -120,14 +129,25 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from nf4_b200.decoder import LLAMA3_8B, LLAMA3_70B
+
     workload = args.workload or ("llama3-8b" if args.gpus == 1 else "llama3-70b")
-    batch = 1 if "8b" in workload else 16
-    tok_s, t_layer, cores = cpu_decode_sample(workload, batch, max(1, args.steps))
+    if workload not in ("llama3-8b", "llama3-70b"):
+        workload = "llama3-8b"
+    cfg, batch, prompt_len = (LLAMA3_8B, 1, 512) if workload == "llama3-8b" else (LLAMA3_70B, 16, 1024)
+    if args.prompt is not None:
+        prompt_len = args.prompt
+    # the CPU arm has one host: it runs the whole (unsharded) model whatever --gpus says; each "step" is a
+    # bounded sample (one decoder layer's linears) scaled to the model, so the run ends within minutes
+    tok_s, t_layer, cores = cpu_decode_sample(workload, batch, max(1, args.steps), min(1, max(0, args.warmup)))
+    D, F = cfg.d_model, cfg.ffn
+    weights = cfg.n_layers * (((cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim) * D + D * cfg.n_heads * cfg.head_dim + 3 * F * D) + cfg.vocab * D
+    config = workload_config(cfg.name, batch, prompt_len, args.gpus, weights * 0.5625 / args.gpus)
     line = {
         "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1000.0 * batch / tok_s, "higher_is_better": True,
         "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{workload}-shape NF4 decode, batch {batch}", "l2": "weights larger than any cache"},
+        "config": config,
         "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"the 4 quantized linears of one decoder layer at M={batch}, median of {max(1, args.steps)} "
                                    f"passes ({t_layer * 1e3:.1f} ms each), scaled to all layers + output head"},
@@ -389,10 +409,7 @@ def run_decode(args):
         "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{cfg.name} NF4 decode, batch {batch}, {prompt_len}-token prompt in the KV cache, greedy",
-                   "parallelism": f"tp{world}", "global_batch": batch, "context": prompt_len,
-                   "l2": f"{step_bytes / 1e9:.2f} GB of weights stream per step per GPU (> L2), no flush needed",
-                   "blocksize": 64, "double_quant": False},
+        "config": workload_config(cfg.name, batch, prompt_len, world, step_bytes),
         "clocks": clocks,
         "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
         "gpu_launches": launches * steps,

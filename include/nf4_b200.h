@@ -150,6 +150,15 @@ int nf4_b200_gemv_decode_fits(int64_t M, int64_t N, int64_t K, int prologue);   
 int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
                          const float* code16, int64_t N, const void* residual, void* y, int prologue,
                          const void* norm_w, float eps, int epilogue, int flags, void* stream);
+/*
+ * Optional hint for the NEXT nf4_b200_gemv_decode call made by this host thread (that call consumes it):
+ * the weight (packed, absmax, N, K) of the launch that will follow it on the same stream.  Each thread
+ * block of the hinted call pulls the head of its share of that weight into L2 once its own loads are in
+ * flight, which keeps HBM busy across the kernel boundary.  Purely a prefetch: results do not change,
+ * a wrong hint only wastes bandwidth.  NULL pointers clear a pending hint.  No counterpart in the reference.
+ */
+int nf4_b200_gemv_decode_next_weight(const uint8_t* packed, const float* absmax, int64_t N, int64_t K);
+
 
 /*
  * Decode-step glue kernels (bf16 tensors, fp32 arithmetic).  In the reference these ops are lowered

@@ -435,6 +435,18 @@ extern "C" int nf4_b200_gemv_fused(const void* x, int64_t M, int64_t K, const ui
     return gemv_typed<__half>(x, (int)M, (int)K, packed, absmax, code16, (int)N, bias, residual, y, s);
 }
 
+// hint for the next nf4_b200_gemv_decode call of this thread (consumed by it)
+static thread_local const uint8_t* t_next_packed = nullptr;
+static thread_local const float* t_next_absmax = nullptr;
+static thread_local int64_t t_next_N = 0, t_next_K = 0;
+
+extern "C" int nf4_b200_gemv_decode_next_weight(const uint8_t* packed, const float* absmax, int64_t N, int64_t K) {
+    NF4_REQUIRE((packed && absmax && N >= 1 && K >= 64 && K % 64 == 0 && N < (1ll << 30) && K < (1ll << 24)) || (!packed && !absmax),
+                NF4_ERR_ARG, "gemv_decode_next_weight: bad hint N=%lld K=%lld", (long long)N, (long long)K);
+    t_next_packed = packed; t_next_absmax = absmax; t_next_N = N; t_next_K = K;
+    return NF4_OK;
+}
+
 extern "C" int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
                                     const float* code16, int64_t N, const void* residual, void* y, int prologue,
                                     const void* norm_w, float eps, int epilogue, int flags, void* stream) {
@@ -450,6 +462,8 @@ extern "C" int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const u
     if (int rc = check_device()) return rc;
     GemvOptions opt;
     opt.prologue = prologue; opt.norm_w = norm_w; opt.eps = eps; opt.epilogue = epilogue; opt.pdl = (flags & 1) != 0;
+    opt.next_packed = t_next_packed; opt.next_absmax = t_next_absmax; opt.next_N = (int)t_next_N; opt.next_K = (int)t_next_K;
+    t_next_packed = nullptr; t_next_absmax = nullptr;
     return gemv_typed<__nv_bfloat16>(x, (int)M, (int)K, packed, absmax, code16, (int)N, nullptr, residual, y,
                                      static_cast<cudaStream_t>(stream), opt);
 }

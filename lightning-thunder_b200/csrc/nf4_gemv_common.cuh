@@ -89,6 +89,11 @@ struct GemvOptions {
     int epilogue = 0;             // 0 none, 1 SwiGLU over (gate, up) row pairs (output has N/2 columns)
     bool pdl = false;             // launch with programmatic stream serialization
     bool dry_run = false;         // plan only: report whether the shape (and prologue) fits
+    // weight the NEXT launch on this stream will read: each CTA pulls the head of its share into L2
+    // once its own loads have been issued (fills the HBM idle time around the kernel boundary)
+    const uint8_t* next_packed = nullptr;
+    const float* next_absmax = nullptr;
+    int next_N = 0, next_K = 0;
 };
 
 // Staged (TMA ring) GEMV: launches and returns NF4_OK (or an error code); returns -1 if the shape does

@@ -32,6 +32,8 @@
 namespace nf4 {
 
 constexpr int SG_MAX_STAGES = 8;
+constexpr int SG_PF_ROWS = 64;          // rows of the next launch's weights a CTA prefetches into L2
+constexpr int SG_PF_ROW_BYTES = 2048;   // ... and bytes of each row (4096 weights)
 constexpr unsigned long long SG_WAIT_LIMIT_NS = 200ull * 1000 * 1000;   // 0.2 s per wait
 
 __device__ unsigned int g_gemv_error[4];   // [0] first error code, [1] block, [2] stage, [3] count
@@ -62,6 +64,10 @@ struct alignas(64) StagedParams {
     // offsets from the start of dynamic shared memory
     int off_bars, off_part, off_x;
     int h_base, h_rem;   // halves of 8 rows per CTA: h_base, plus one for the first h_rem CTAs
+    // L2 prefetch of the next launch's weights (null: none): same row split, applied to its N
+    const uint8_t* pf_packed;
+    const float* pf_absmax;
+    int pf_N, pf_row_bytes, pf_am_row_bytes, pf_h_base, pf_h_rem;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -295,6 +301,18 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                 }
             }
             tile0 += nt_here;
+        }
+        if (p.pf_packed) {
+            // every load of this launch is in flight: pull the head of this CTA's share of the next
+            // launch's weights into L2 (first SG_PF_ROWS rows, up to SG_PF_ROW_BYTES of each)
+            const int f0 = (bid * p.pf_h_base + min(bid, p.pf_h_rem)) * 8;
+            const int f1 = min(f0 + (p.pf_h_base + (bid < p.pf_h_rem ? 1 : 0)) * 8, p.pf_N);
+            const uint32_t wb = (uint32_t)min(p.pf_row_bytes, SG_PF_ROW_BYTES);
+            const uint32_t ab = (uint32_t)min(p.pf_am_row_bytes, SG_PF_ROW_BYTES / 8) & ~15u;
+            for (int row = f0 + lane; row < min(f1, f0 + SG_PF_ROWS); row += 32) {
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_packed + (int64_t)row * p.pf_row_bytes), "r"(wb) : "memory");
+                if (ab) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<const uint8_t*>(p.pf_absmax) + (int64_t)row * p.pf_am_row_bytes), "r"(ab) : "memory");
+            }
         }
         return;
     }
@@ -707,6 +725,20 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     p.M = M; p.N = N; p.K = K; p.KB = KB; p.SB = SB; p.nseg = KB / SB;
     p.h_base = H / grid;
     p.h_rem = H % grid;
+    p.pf_packed = nullptr; p.pf_absmax = nullptr; p.pf_N = 0; p.pf_row_bytes = 0; p.pf_am_row_bytes = 0; p.pf_h_base = 0; p.pf_h_rem = 0;
+    if (opt.next_packed && opt.next_absmax && opt.next_N > 0 && opt.next_K >= 64 && opt.next_K % 64 == 0 &&
+        reinterpret_cast<uintptr_t>(opt.next_packed) % 16 == 0 && reinterpret_cast<uintptr_t>(opt.next_absmax) % 16 == 0 &&
+        (opt.next_K / 64) % 4 == 0) {
+        // the next launch deals its rows out the same way over (up to) the same number of CTAs
+        const int Hn = (opt.next_N + 7) / 8;
+        int gn = sms;
+        if (gn > (Hn + 1) / 2) gn = (Hn + 1) / 2;
+        if (gn == grid) {
+            p.pf_packed = opt.next_packed; p.pf_absmax = opt.next_absmax; p.pf_N = opt.next_N;
+            p.pf_row_bytes = opt.next_K / 2; p.pf_am_row_bytes = opt.next_K / 64 * 4;
+            p.pf_h_base = Hn / gn; p.pf_h_rem = Hn % gn;
+        }
+    }
     p.RS = SB * 32 + 32;
     p.AS = SB * 4 + 16;
     p.stage_bytes = 16 * p.RS + 16 * p.AS;

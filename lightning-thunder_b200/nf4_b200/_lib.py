@@ -30,6 +30,7 @@ SIGNATURES = {
     "nf4_b200_gemv": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "nf4_b200_gemm": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int,
                                _c_ptr, _c_i64, _c_ptr]),
+    "nf4_b200_gemv_decode_next_weight": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64]),
     "nf4_b200_gemm_workspace_bytes": (_c_i64, [_c_i64, _c_i64, _c_i64]),
     "nf4_b200_gemm_decode": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_int,
                                       _c_ptr, _c_i64, _c_int, _c_ptr]),

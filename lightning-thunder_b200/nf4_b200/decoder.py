@@ -72,7 +72,7 @@ def _seeded_normal(shape, seed: int, device, std=0.02) -> torch.Tensor:
 class NF4Decoder:
     def __init__(self, cfg: DecoderConfig, batch: int, max_seq: int, device="cuda:0", seed: int = 0, tp_rank: int = 0,
                  tp_size: int = 1, group=None, attn_splits: int | None = None, fused: bool = True, pdl: bool = True,
-                 tensor_core_from: int = 17):
+                 tensor_core_from: int = 17, prefetch_next: bool = True):
         assert cfg.head_dim == 128, "the attention kernel is written for head_dim 128"
         assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.ffn % (64 * tp_size) == 0
         assert cfg.vocab % tp_size == 0 and batch <= 16
@@ -93,6 +93,9 @@ class NF4Decoder:
         # thread blocks, residual / SwiGLU epilogues) with RMSNorm as a separate small kernel before it;
         # up to 16 sequences the GEMV measures faster on every layer shape, so that is the default
         self.tensor_core = fused and batch >= tensor_core_from
+        # every GEMV of the fused step tells the library which weight the next launch streams, so the head
+        # of it is pulled into L2 across the kernel boundary
+        self.prefetch_next = fused and prefetch_next
         self.Hq = cfg.n_heads // tp_size
         self.Hkv = cfg.n_kv_heads // tp_size
         self.F = cfg.ffn // tp_size
@@ -183,7 +186,8 @@ class NF4Decoder:
     def _all_reduce(self, t):
         torch.distributed.all_reduce(t, group=self.group)
 
-    def _linear_decode(self, x, w: NF4Weight, y, residual=None, prologue=0, norm_w=None, swiglu=False, stream=None):
+    def _linear_decode(self, x, w: NF4Weight, y, residual=None, prologue=0, norm_w=None, swiglu=False, stream=None,
+                       next_w: NF4Weight | None = None):
         """GEMV with an optional fused prologue (RMSNorm) and epilogue (SwiGLU over interleaved gate/up
         rows); falls back to separate glue kernels around a plain GEMV when the shape does not fit."""
         lib, cfg, B = self.lib, self.cfg, self.B
@@ -219,6 +223,9 @@ class NF4Decoder:
                 x = self.h
             self._n += 1
             prologue, norm_w = 0, None
+        if next_w is not None and self.prefetch_next:
+            ck(lib.nf4_b200_gemv_decode_next_weight(next_w.packed.data_ptr(), next_w.absmax.data_ptr(), next_w.N, next_w.K),
+               "nf4_b200_gemv_decode_next_weight")
         ev = self._ev_begin()
         ck(lib.nf4_b200_gemv_decode(x.data_ptr(), B, w.K, w.packed.data_ptr(), w.absmax.data_ptr(), w.code.data_ptr(), w.N,
                                     residual.data_ptr() if residual is not None else None, y.data_ptr(), prologue,
@@ -257,25 +264,29 @@ class NF4Decoder:
         ck(lib.nf4_b200_embed(self.ids_in.data_ptr(), self.embed.data_ptr(), self.x.data_ptr(), B, D, cfg.vocab, st), "embed")
         self._n += 1
         for li, layer in enumerate(self.layers):
-            self._linear_decode(self.x, layer["qkv"], self.qkv, prologue=1, norm_w=layer["norm1"], stream=st)
+            after = self.layers[li + 1]["qkv"] if li + 1 < len(self.layers) else self.lm_head
+            self._linear_decode(self.x, layer["qkv"], self.qkv, prologue=1, norm_w=layer["norm1"], stream=st, next_w=layer["o"])
             ck(lib.nf4_b200_attn_decode_fused(self.qkv.data_ptr(), self.positions.data_ptr(), self.k_cache[li].data_ptr(),
                                               self.v_cache[li].data_ptr(), self.attn.data_ptr(), self.attn_ws.data_ptr(),
                                               self.attn_counters.data_ptr(), B, self.Hq, self.Hkv, Dh, self.S,
                                               self.attn_splits, cfg.rope_theta, self.flags, st), "attn_decode_fused")
             self._n += 1
             if tp:
-                self._linear_decode(self.attn, layer["o"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st)
+                self._linear_decode(self.attn, layer["o"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st,
+                                    next_w=layer["gu"])
                 self._all_reduce(self.part)
                 self.x, self.part = self.part, self.x
             else:
-                self._linear_decode(self.attn, layer["o"], self.x, residual=self.x, stream=st)
-            self._linear_decode(self.x, layer["gu"], self.h, prologue=1, norm_w=layer["norm2"], swiglu=True, stream=st)
+                self._linear_decode(self.attn, layer["o"], self.x, residual=self.x, stream=st, next_w=layer["gu"])
+            self._linear_decode(self.x, layer["gu"], self.h, prologue=1, norm_w=layer["norm2"], swiglu=True, stream=st,
+                                next_w=layer["down"])
             if tp:
-                self._linear_decode(self.h, layer["down"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st)
+                self._linear_decode(self.h, layer["down"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st,
+                                    next_w=after)
                 self._all_reduce(self.part)
                 self.x, self.part = self.part, self.x
             else:
-                self._linear_decode(self.h, layer["down"], self.x, residual=self.x, stream=st)
+                self._linear_decode(self.h, layer["down"], self.x, residual=self.x, stream=st, next_w=after)
         self._linear_decode(self.x, self.lm_head, self.logits, prologue=1, norm_w=self.final_norm, stream=st)
         ck(lib.nf4_b200_argmax(self.logits.data_ptr(), self.ids_out.data_ptr(), B, self.V, st), "argmax")
         self._n += 1
@@ -288,11 +299,13 @@ class NF4Decoder:
         st = ctypes.c_void_p(torch.cuda.current_stream(self.dev).cuda_stream)
         self._n = 0
         tp = self.tp_size > 1
-        for layer in self.layers:
-            self._linear_decode(self.x, layer["qkv"], self.qkv, prologue=1, norm_w=layer["norm1"], stream=st)
-            self._linear_decode(self.attn, layer["o"], self.part if tp else self.x, residual=self.x, stream=st)
-            self._linear_decode(self.x, layer["gu"], self.h, prologue=1, norm_w=layer["norm2"], swiglu=True, stream=st)
-            self._linear_decode(self.h, layer["down"], self.part if tp else self.x, residual=self.x, stream=st)
+        for li, layer in enumerate(self.layers):
+            after = self.layers[li + 1]["qkv"] if li + 1 < len(self.layers) else self.lm_head
+            self._linear_decode(self.x, layer["qkv"], self.qkv, prologue=1, norm_w=layer["norm1"], stream=st, next_w=layer["o"])
+            self._linear_decode(self.attn, layer["o"], self.part if tp else self.x, residual=self.x, stream=st, next_w=layer["gu"])
+            self._linear_decode(self.x, layer["gu"], self.h, prologue=1, norm_w=layer["norm2"], swiglu=True, stream=st,
+                                next_w=layer["down"])
+            self._linear_decode(self.h, layer["down"], self.part if tp else self.x, residual=self.x, stream=st, next_w=after)
         self._linear_decode(self.x, self.lm_head, self.logits, prologue=1, norm_w=self.final_norm, stream=st)
 
     def _finish_step(self) -> None:

@@ -282,3 +282,39 @@ def test_gemm_decode_epilogues(nf4_code_np, flags, M, N, K):
         torch.testing.assert_close(h.float(), href, rtol=3e-2, atol=1e-2)
     torch.cuda.synchronize()
     assert _lib.device_error()[0] == 0
+
+
+def test_next_weight_hint_changes_nothing(nf4_code_np):
+    """nf4_b200_gemv_decode_next_weight is a pure L2 prefetch: same bytes out with a right hint, a hint
+    for another shape, or none; the hint is consumed by one call."""
+    import ctypes
+
+    import nf4_b200
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    N, K = 4096, 4096
+    w = seeded_weight((N, K), 31).cuda()
+    w2 = seeded_weight((6144, K), 32).cuda()
+    x = seeded_act((1, K), 33).cuda()
+    packed, qs = nf4_b200.quantize_4bit(w)
+    packed2, qs2 = nf4_b200.quantize_4bit(w2)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def run(hint):
+        y = torch.empty((1, N), dtype=torch.bfloat16, device="cuda")
+        if hint is not None:
+            _lib.check(lib.nf4_b200_gemv_decode_next_weight(*hint), "hint")
+        _lib.check(lib.nf4_b200_gemv_decode(x.data_ptr(), 1, K, packed.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N,
+                                            None, y.data_ptr(), 0, None, 0.0, 0, 0, st), "gemv_decode")
+        return y
+
+    base = run(None)
+    assert torch.equal(run((packed2.data_ptr(), qs2.absmax.data_ptr(), 6144, K)), base)
+    assert torch.equal(run((packed.data_ptr(), qs.absmax.data_ptr(), N, K)), base)
+    assert torch.equal(run((packed2.data_ptr(), qs2.absmax.data_ptr(), 40, K)), base)     # other grid: ignored
+    assert torch.equal(run(None), base)
+    assert lib.nf4_b200_gemv_decode_next_weight(packed.data_ptr(), qs.absmax.data_ptr(), N, 100) != 0   # K % 64 != 0
+    assert lib.nf4_b200_gemv_decode_next_weight(None, None, 0, 0) == 0
+    torch.cuda.synchronize()
+    assert _lib.device_error()[0] == 0
