@@ -713,11 +713,20 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     int grid = sms;
     if (grid > (H + 1) / 2) grid = (H + 1) / 2;
     const int tiles = ((H + grid - 1) / grid + 1) / 2;
-    int TG = NT == 1 ? 4 : 2;
+    // 16 compute warps; 8 for two column tiles whose activations stay in global memory (more than fit
+    // below the table): every group of tiles re-reads the activations from L2, so the groups are made
+    // 4 tiles tall, which needs the registers of the 8-warp shape
+    int CW = 16;
+    if (NT == 2 && (int64_t)M * K * 2 > 40 * 1024) CW = 8;
+    if (const char* env = getenv("NF4_GEMV_CW")) {
+        const int v = atoi(env);
+        if (v == 8 || v == 16) CW = v;
+    }
+    int TG = (NT == 1 || CW == 8) ? 4 : 2;
     while (TG > 1 && TG / 2 >= tiles) TG /= 2;
     if (const char* env = getenv("NF4_GEMV_TG")) {
         const int v = atoi(env);
-        if (v == 1 || v == 2 || (v == 4 && NT == 1)) TG = v;
+        if (v == 1 || v == 2 || (v == 4 && (NT == 1 || CW == 8))) TG = v;
     }
 
     StagedParams p;
@@ -751,11 +760,6 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     const int low_cap = LUT_WINDOW - 2048;           // leaves room for the window's start offset
     p.off_bars = 0;
     p.off_part = 256;
-    int CW = 16;
-    if (const char* env = getenv("NF4_GEMV_CW")) {
-        const int v = atoi(env);
-        if (v == 8 || v == 16) CW = v;
-    }
     const int part_bytes = CW * TG * M * 16 * 4;
     p.off_x = (p.off_part + part_bytes + 127) & ~127;
     if (p.off_x > low_cap) return -1;
@@ -786,6 +790,7 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         if (TG == 2) NF4_SG(1, 2);
         NF4_SG(1, 1);
     } else {
+        if (TG == 4) return launch_staged<T, 2, 4, 8>(p, grid, stream);
         if (TG == 2) NF4_SG(2, 2);
         NF4_SG(2, 1);
     }
