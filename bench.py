@@ -81,6 +81,12 @@ class ClockSampler:
 # reference arm / CPU baseline: the oracle's linears on the host cores
 # --------------------------------------------------------------------------------------------
 
+# DRAM traffic of the fused dequant-GEMV relative to its algorithmic bytes, from one ncu capture of the kernel
+# (N=32064, K=4096, M=1: 73.95 MB read + 0.93 MB written against 73.95 MB algorithmic); the kernel streams
+# every weight byte exactly once, so traffic grows in proportion to N*K.
+NCU_TRAFFIC_RATIO = 74.875 / 73.948
+
+
 def workload_config(name: str, batch: int, prompt_len: int, world: int, step_bytes: float) -> dict:
     """The `config` object of the JSON line; both arms print the same one."""
     return {"workload": f"{name} NF4 decode, batch {batch}, {prompt_len}-token prompt in the KV cache, greedy",
@@ -414,7 +420,10 @@ def run_decode(args):
         "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
         "gpu_launches": launches * steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / peaks["hbm_gbs"], "peak_source": src, "traffic": None,
+                     "frac": achieved / peaks["hbm_gbs"], "peak_source": src,
+                     "traffic": NCU_TRAFFIC_RATIO * sum(gemv_bytes) / len(gemv_bytes),
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 32064x4096, M=1 "
+                                       "(74.88 MB for 73.95 MB algorithmic), scaled by algorithmic bytes",
                      "kernel": "gemv_staged_kernel (fused NF4 dequant-GEMV)", "launches_per_step": len(ev),
                      "avg_launch_us": sum(gemv_us) / len(gemv_us), "algorithmic_bytes_per_launch": sum(gemv_bytes) / len(gemv_bytes),
                      "frac_of_8TBps": achieved / 8000.0,

@@ -21,7 +21,7 @@ from dataclasses import dataclass
 
 import torch
 
-from . import _lib
+from . import _lib, parallel
 from .functional import nf4_code, quantize_4bit
 
 
@@ -74,8 +74,8 @@ class NF4Decoder:
                  tp_size: int = 1, group=None, attn_splits: int | None = None, fused: bool = True, pdl: bool = True,
                  tensor_core_from: int = 17, prefetch_next: bool = True):
         assert cfg.head_dim == 128, "the attention kernel is written for head_dim 128"
-        assert cfg.n_heads % tp_size == 0 and cfg.n_kv_heads % tp_size == 0 and cfg.ffn % (64 * tp_size) == 0
-        assert cfg.vocab % tp_size == 0 and batch <= 16
+        parallel.check_shardable(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab, tp_size)
+        assert batch <= 16
         self.cfg, self.B, self.S = cfg, batch, max_seq
         self.dev = torch.device(device)
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
@@ -110,7 +110,7 @@ class NF4Decoder:
                 self.layers.append(self._make_layer(base))
             self.final_norm = torch.ones(D, device=dev, dtype=bf)
             w = _seeded_normal((cfg.vocab, D), seed * 1000003 + 7, dev)
-            self.lm_head = NF4Weight(w[self.tp_rank * self.V:(self.tp_rank + 1) * self.V])
+            self.lm_head = NF4Weight(parallel.shard_rows(w, self.tp_rank, tp_size))
             del w
             L, B, S = cfg.n_layers, batch, max_seq
             self.k_cache = torch.zeros((L, B, self.Hkv, S, Dh), device=dev, dtype=bf)
@@ -147,16 +147,15 @@ class NF4Decoder:
         wq = _seeded_normal((cfg.n_heads * Dh, D), base + 1, dev)
         wk = _seeded_normal((cfg.n_kv_heads * Dh, D), base + 2, dev)
         wv = _seeded_normal((cfg.n_kv_heads * Dh, D), base + 3, dev)
-        hq, hk = self.Hq * Dh, self.Hkv * Dh
-        qkv = torch.cat([wq[r * hq:(r + 1) * hq], wk[r * hk:(r + 1) * hk], wv[r * hk:(r + 1) * hk]], dim=0)
+        qkv = parallel.shard_qkv(wq, wk, wv, r, tp)
         del wq, wk, wv
-        wo = _seeded_normal((D, cfg.n_heads * Dh), base + 4, dev)[:, r * hq:(r + 1) * hq].contiguous()
+        wo = parallel.shard_cols(_seeded_normal((D, cfg.n_heads * Dh), base + 4, dev), r, tp)
         wg = _seeded_normal((cfg.ffn, D), base + 5, dev)
         wu = _seeded_normal((cfg.ffn, D), base + 6, dev)
         # rows interleaved (gate_0, up_0, gate_1, up_1, ...) so the GEMV epilogue can apply SwiGLU
-        gu = torch.stack([wg[r * self.F:(r + 1) * self.F], wu[r * self.F:(r + 1) * self.F]], dim=1).reshape(2 * self.F, D)
+        gu = parallel.shard_gate_up(wg, wu, r, tp)
         del wg, wu
-        wd = _seeded_normal((D, cfg.ffn), base + 7, dev)[:, r * self.F:(r + 1) * self.F].contiguous()
+        wd = parallel.shard_cols(_seeded_normal((D, cfg.ffn), base + 7, dev), r, tp)
         layer = {
             "qkv": NF4Weight(qkv), "o": NF4Weight(wo), "gu": NF4Weight(gu), "down": NF4Weight(wd),
             "norm1": torch.ones(D, device=dev, dtype=torch.bfloat16),
@@ -311,12 +310,9 @@ class NF4Decoder:
     def _finish_step(self) -> None:
         if self.tp_size > 1:
             # candidates (value, global index) of every rank; the first maximum in rank order wins
-            local = self.ids_out
-            self.cand[:, 0] = self.logits.gather(1, local.view(-1, 1)).view(-1).float()
-            self.cand[:, 1] = (local + self.tp_rank * self.V).float()
+            self.cand.copy_(parallel.local_candidates(self.logits, self.ids_out, self.tp_rank, self.V))
             torch.distributed.all_gather_into_tensor(self.cand_all, self.cand, group=self.group)
-            best = self.cand_all[:, :, 0].argmax(dim=0)
-            self.ids_out.copy_(self.cand_all[:, :, 1].gather(0, best.view(1, -1)).view(-1).long())
+            self.ids_out.copy_(parallel.merge_candidates(self.cand_all))
         self.positions.add_(1)
         self.launches_per_step = self._n
 
