@@ -214,3 +214,94 @@ def test_llama_shaped_module_gpu_matches_oracle_backend(monkeypatch):
     want = jc(tokens)
     want0 = (want[0] if isinstance(want, tuple) else want).float()
     torch.testing.assert_close(got0, want0, rtol=5e-2, atol=5e-2)
+
+
+def _meta_mlp(dtype):
+    with torch.device("meta"):
+        return torch.nn.Sequential(torch.nn.Linear(512, 1024), torch.nn.GELU(), torch.nn.Linear(1024, 512)).to(dtype).eval().requires_grad_(False)
+
+
+def test_materialization_routes_cpu(cpu_backend):
+    """The three ways the reference builds a quantized module give the same parameters and outputs
+    (thunder/tests/test_transforms.py:116-186): from real weights; from a meta-device module filled from the
+    ORIGINAL state dict (quantized while loading, submodule by submodule); from a meta-device module
+    filled from the TRANSFORMED (already quantized) state dict."""
+    from thunder.transforms import MaterializationTransform
+
+    ex = get_nf4_executor()
+    dtype = torch.bfloat16
+    ref = _mlp(dtype)
+    jm_ref = thunder.jit(ref, transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    init_orig = MaterializationTransform.init_from_original_state_dict(ref.state_dict())
+    jm = thunder.jit(_meta_mlp(dtype), transforms=[NF4LinearQuant4bit(), MaterializationTransform("cpu", init=init_orig)],
+                     executors=(ex,))
+    init_tr = MaterializationTransform.init_from_transformed_state_dict(jm_ref.state_dict())
+    jm2 = thunder.jit(_meta_mlp(dtype), transforms=[NF4LinearQuant4bit(), MaterializationTransform("cpu", init=init_tr)],
+                      executors=(ex,))
+    x = torch.randn(2, 512, dtype=dtype)
+    expected = jm_ref(x)
+    assert torch.equal(jm(x), expected) and torch.equal(jm2(x), expected)
+    for n, p in jm_ref.named_parameters():
+        assert torch.equal(jm.get_parameter(n), p), n
+        assert torch.equal(jm2.get_parameter(n), p), n
+        assert jm.get_parameter(n).device.type == "cpu"
+    assert set(jm.state_dict()) == set(jm_ref.state_dict())
+
+
+def test_materialization_from_module_init_with_tied_weights_cpu(cpu_backend):
+    """Meta-device module materialised by re-running the modules' own initialisers, with a tied Linear(2, 2)
+    (numel 4 < blocksize) -- thunder/tests/test_transforms.py:293-344."""
+    from thunder.transforms import MaterializationTransform
+
+    def get_model():
+        m0 = torch.nn.Linear(2, 2)
+        with torch.device("meta"):      # not to change the rng state
+            m4 = torch.nn.Linear(2, 2)
+        m4.weight, m4.bias = m0.weight, m0.bias
+        return torch.nn.Sequential(m0, torch.nn.GELU(), torch.nn.Linear(2, 2), torch.nn.GELU(), m4).eval().requires_grad_(False)
+
+    ex = get_nf4_executor()
+    torch.manual_seed(1234)
+    m_ref = get_model()
+    inp = torch.randn(3, 2)
+    jm_ref = thunder.jit(m_ref, transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    torch.manual_seed(1234)
+    with torch.device("meta"):
+        m = get_model()
+    jm = thunder.jit(m, transforms=[NF4LinearQuant4bit(),
+                                    MaterializationTransform("cpu", init=MaterializationTransform.init_from_original_module_init())],
+                     executors=(ex,))
+    torch.testing.assert_close(jm(inp), jm_ref(inp))
+    assert jm_ref._get_shared_names()["0.weight"] == {"0.weight", "4.weight"}
+    assert jm._get_shared_names()["0.weight"] == {"0.weight", "4.weight"}
+
+
+@pytest.mark.gpu
+def test_materialization_routes_gpu():
+    """The same three routes on the kernels: a meta-device module is materialised on the GPU and its
+    weights are quantized there, shard by shard of the state dict (thunder/tests/test_transforms.py:116-186)."""
+    from thunder.transforms import MaterializationTransform
+
+    ex = get_nf4_executor()
+    dtype = torch.bfloat16
+    ref = _mlp(dtype, "cuda")
+    jm_ref = thunder.jit(ref, transforms=[NF4LinearQuant4bit()], executors=(ex,))
+
+    def meta():
+        m = _meta_mlp(dtype)
+        for p in m.parameters():
+            p._thunder_device = torch.device("cuda")
+        return m
+
+    init_orig = MaterializationTransform.init_from_original_state_dict(ref.state_dict())
+    jm = thunder.jit(meta(), transforms=[NF4LinearQuant4bit(), MaterializationTransform("cuda", init=init_orig)], executors=(ex,))
+    init_tr = MaterializationTransform.init_from_transformed_state_dict(jm_ref.state_dict())
+    jm2 = thunder.jit(meta(), transforms=[NF4LinearQuant4bit(), MaterializationTransform("cuda", init=init_tr)], executors=(ex,))
+    x = torch.randn(2, 512, dtype=dtype, device="cuda")
+    expected = jm_ref(x)
+    assert torch.equal(jm(x), expected) and torch.equal(jm2(x), expected)
+    for n, p in jm_ref.named_parameters():
+        assert torch.equal(jm.get_parameter(n), p), n
+        assert torch.equal(jm2.get_parameter(n), p), n
+        assert jm.get_parameter(n).device.type == "cuda"
+    torch.testing.assert_close(expected.float(), ref(x).float(), atol=2e-1, rtol=2e-1)
