@@ -116,6 +116,164 @@ __device__ __forceinline__ void merge_splits_warp(const float* __restrict__ base
     *reinterpret_cast<__nv_bfloat162*>(dst + lane * 4 + 2) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
 }
 
+// ---- attention over a range of cached positions on the tensor cores ------------------------------
+// One warp walks tiles of 16 positions: K and V rows are copied coalesced into the warp's shared-memory
+// tile (16 rows x 256 B, 16-byte chunks XOR-swizzled with the row so ldmatrix is conflict-free), scores
+// S = Q.K^T come from mma.sync m16n8k16 with the G <= 8 query heads of the group as rows 0..G-1 of the A
+// operand (rows 8..15 stay zero), the online softmax runs on the accumulator fragments (a quad of lanes
+// owns a head's 16 scores), and O += P.V takes P straight from those fragments and V through
+// ldmatrix.trans.  Per position: 2 MMAs instead of 64 FMAs and 40 shuffles.
+// Results of the warp: w_m[h], w_l[h], w_o[h][128] (unnormalised), in the warp's tile memory (w_o aliases
+// the tiles, which are dead by then).
+constexpr int AT_TILE = 16;                 // positions per tile
+constexpr int AT_TILE_BYTES = AT_TILE * 256;
+constexpr int AT_WARP_BYTES = 4 * AT_TILE_BYTES;     // per warp: two buffers of (K tile + V tile)
+// dynamic shared memory of the attention kernels: 4 warps of tiles, the group's queries, the warps' max / sum, a flag
+constexpr int AT_SMEM_BYTES = 4 * AT_WARP_BYTES + 8 * 128 * 2 + 2 * 4 * 8 * 4 + 16;
+
+__device__ __forceinline__ void at_ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void at_ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void at_mma(float (&d)[2], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    // rows 8..15 of A (a1, a3) are zero, so rows 8..15 of the result are zero too and are not kept
+    float x2, x3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%10,%10};"
+                 : "+f"(d[0]), "+f"(d[1]), "=f"(x2), "=f"(x3) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(0.0f));
+}
+__device__ __forceinline__ void at_cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    // src_bytes = 0 fills the 16 bytes with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// q_s: bf16 [G][128] in shared memory (rotated, not scaled).  pos_new >= 0: that row of the cache is being
+// written by this very kernel; its values come from knew/vnew (this lane's dims 4*lane..4*lane+3) instead.
+template <int G>
+__device__ __forceinline__ void attend_range(const bf16* __restrict__ kb, const bf16* __restrict__ vb, int s_begin, int s_end,
+                                             int pos_new, const float (&knew)[4], const float (&vnew)[4],
+                                             const bf16* q_s, float scale, uint8_t* tiles, float* w_m, float* w_l, float* w_o,
+                                             int warp, int lane) {
+    const int g = lane >> 2, q = lane & 3;
+    const uint32_t k_u32 = (uint32_t)__cvta_generic_to_shared(tiles);
+    // A fragments of Q for the 8 k-steps of 16 dims
+    uint32_t qa0[8], qa2[8];
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        qa0[kk] = g < G ? *reinterpret_cast<const uint32_t*>(q_s + g * 128 + 16 * kk + 2 * q) : 0u;
+        qa2[kk] = g < G ? *reinterpret_cast<const uint32_t*>(q_s + g * 128 + 16 * kk + 8 + 2 * q) : 0u;
+    }
+    float m = -FLT_MAX, l = 0.0f;
+    float o[16][2];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) { o[t][0] = 0.0f; o[t][1] = 0.0f; }
+
+    // tiles are double-buffered: the asynchronous copy of the next tile runs under the MMAs of this one
+    auto issue = [&](int s0, int buf) {
+        const uint32_t kd = k_u32 + (uint32_t)(buf * 2 * AT_TILE_BYTES), vd = kd + AT_TILE_BYTES;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int idx = it * 32 + lane, r = idx >> 4, c = idx & 15, sp = s0 + r;
+            const bool ok = sp < s_end && sp != pos_new;
+            const int64_t off = ok ? (int64_t)sp * 128 + c * 8 : 0;
+            const uint32_t dst = (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4));
+            at_cp_async16(kd + dst, kb + off, ok ? 16u : 0u);
+            at_cp_async16(vd + dst, vb + off, ok ? 16u : 0u);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int buf = 0;
+    const int first = s_begin + warp * AT_TILE;
+    if (first < s_end) issue(first, 0);
+    for (int s0 = first; s0 < s_end; s0 += 4 * AT_TILE, buf ^= 1) {
+        const int next = s0 + 4 * AT_TILE;
+        if (next < s_end) {
+            issue(next, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncwarp();
+        uint8_t* const kt = tiles + buf * 2 * AT_TILE_BYTES;
+        const uint32_t kt_u32 = k_u32 + (uint32_t)(buf * 2 * AT_TILE_BYTES), vt_u32 = kt_u32 + AT_TILE_BYTES;
+        if (pos_new >= s0 && pos_new < s0 + AT_TILE && pos_new < s_end) {
+            const int r = pos_new - s0;
+            const int off = r * 256 + (((lane >> 1) ^ (r & 7)) << 4) + (lane & 1) * 8;
+            *reinterpret_cast<uint2*>(kt + off) = make_uint2(at_pack(knew[0], knew[1]), at_pack(knew[2], knew[3]));
+            *reinterpret_cast<uint2*>(kt + AT_TILE_BYTES + off) = make_uint2(at_pack(vnew[0], vnew[1]), at_pack(vnew[2], vnew[3]));
+            __syncwarp();
+        }
+        // ---- S = Q.K^T: two n-tiles of 8 positions, 8 k-steps
+        float sc[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            sc[j][0] = 0.0f; sc[j][1] = 0.0f;
+#pragma unroll
+            for (int kp = 0; kp < 4; ++kp) {
+                const int r = 8 * j + (lane & 7), chunk = 4 * kp + (lane >> 3);
+                uint32_t b[4];
+                at_ldmatrix_x4(kt_u32 + (uint32_t)(r * 256 + ((chunk ^ (r & 7)) << 4)), b);
+                at_mma(sc[j], qa0[2 * kp], qa2[2 * kp], b[0], b[1]);
+                at_mma(sc[j], qa0[2 * kp + 1], qa2[2 * kp + 1], b[2], b[3]);
+            }
+        }
+        // ---- online softmax on row g (this quad): columns 8j + 2q, 8j + 2q + 1
+        float p[2][2];
+        float tmax = -FLT_MAX;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int sp = s0 + 8 * j + 2 * q + e;
+                p[j][e] = sp < s_end ? sc[j][e] * scale : -FLT_MAX;
+                tmax = fmaxf(tmax, p[j][e]);
+            }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float mn = fmaxf(m, tmax);
+        const float corr = __expf(m - mn);
+        float tsum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                p[j][e] = p[j][e] > -FLT_MAX ? __expf(p[j][e] - mn) : 0.0f;
+                tsum += p[j][e];
+            }
+        tsum += __shfl_xor_sync(0xffffffffu, tsum, 1);
+        tsum += __shfl_xor_sync(0xffffffffu, tsum, 2);
+        l = l * corr + tsum;
+        m = mn;
+        const uint32_t pa0 = at_pack(p[0][0], p[0][1]), pa2 = at_pack(p[1][0], p[1][1]);
+        // ---- O = O * corr + P.V: 16 n-tiles of 8 dims, one k-step of 16 positions
+#pragma unroll
+        for (int tp = 0; tp < 8; ++tp) {
+            const int mi = lane >> 3, r = (mi & 1) * 8 + (lane & 7), chunk = 2 * tp + (mi >> 1);
+            uint32_t b[4];
+            at_ldmatrix_x4_trans(vt_u32 + (uint32_t)(r * 256 + ((chunk ^ (r & 7)) << 4)), b);
+            o[2 * tp][0] *= corr; o[2 * tp][1] *= corr;
+            o[2 * tp + 1][0] *= corr; o[2 * tp + 1][1] *= corr;
+            at_mma(o[2 * tp], pa0, pa2, b[0], b[1]);
+            at_mma(o[2 * tp + 1], pa0, pa2, b[2], b[3]);
+        }
+        __syncwarp();       // the other buffer is refilled at the top of the next iteration
+    }
+    __syncwarp();
+    if (g < G) {
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+            w_o[g * 128 + 8 * t + 2 * q] = o[t][0];
+            w_o[g * 128 + 8 * t + 2 * q + 1] = o[t][1];
+        }
+        if (q == 0) { w_m[g] = m; w_l[g] = l; }
+    }
+}
+
 // ---- single-query attention over the cache, split along the sequence --------------------------
 // One CTA per (kv head, batch row, split).  Dh = 128: a lane owns 4 dims.  G = Hq/Hkv query heads
 // share the K/V stream.  Partial results (max, sum, unnormalised output) go to `ws`
@@ -133,53 +291,22 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
     const int s_end = min(len, s_begin + chunk);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-    float qv[G][4];
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-        const bf16* qp = q + ((int64_t)b * Hq + hk * G + h) * Dh + lane * 4;
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qp));
-        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qp + 2));
-        qv[h][0] = a.x * scale; qv[h][1] = a.y * scale; qv[h][2] = c.x * scale; qv[h][3] = c.y * scale;
-    }
-    float m[G], l[G], o[G][4];
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-        m[h] = -FLT_MAX; l[h] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[h][e] = 0.0f;
-    }
+    // per warp: two buffers of K tile + V tile, reused for the warp's unnormalised output [G][128] fp32
+    extern __shared__ __align__(128) uint8_t at_smem[];
+    uint8_t (*s_tiles)[AT_WARP_BYTES] = reinterpret_cast<uint8_t (*)[AT_WARP_BYTES]>(at_smem);
+    bf16* const s_q = reinterpret_cast<bf16*>(at_smem + 4 * AT_WARP_BYTES);
+    float (*s_m)[8] = reinterpret_cast<float (*)[8]>(at_smem + 4 * AT_WARP_BYTES + 2048);
+    float (*s_l)[8] = s_m + 4;
+    for (int i = threadIdx.x; i < G * Dh / 2; i += 128)
+        reinterpret_cast<uint32_t*>(s_q)[i] = reinterpret_cast<const uint32_t*>(q + ((int64_t)b * Hq + hk * G) * Dh)[i];
+    __syncthreads();
     const bf16* kb = k_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
     const bf16* vb = v_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
-    for (int s = s_begin + warp; s < s_end; s += 4) {
-        const uint2 kr = *reinterpret_cast<const uint2*>(kb + (int64_t)s * Dh + lane * 4);
-        const uint2 vr = *reinterpret_cast<const uint2*>(vb + (int64_t)s * Dh + lane * 4);
-        const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.x));
-        const float2 k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr.y));
-        const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.x));
-        const float2 v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr.y));
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float sc = qv[h][0] * k0.x + qv[h][1] * k0.y + qv[h][2] * k1.x + qv[h][3] * k1.y;
-            sc = warp_sum(sc);
-            const float mn = fmaxf(m[h], sc);
-            const float corr = __expf(m[h] - mn);
-            const float pw = __expf(sc - mn);
-            l[h] = l[h] * corr + pw;
-            o[h][0] = o[h][0] * corr + pw * v0.x;
-            o[h][1] = o[h][1] * corr + pw * v0.y;
-            o[h][2] = o[h][2] * corr + pw * v1.x;
-            o[h][3] = o[h][3] * corr + pw * v1.y;
-            m[h] = mn;
-        }
-    }
+    const float none[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    attend_range<G>(kb, vb, s_begin, s_end, -1, none, none, s_q, scale, s_tiles[warp], s_m[warp], s_l[warp],
+                    reinterpret_cast<float*>(s_tiles[warp]), warp, lane);
     // merge the 4 warps
-    __shared__ float s_m[4][G], s_l[4][G], s_o[4][G][Dh];
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-        if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s_o[warp][h][lane * 4 + e] = o[h][e];
-    }
+    auto s_o = [&](int w, int h, int d) -> float { return reinterpret_cast<const float*>(s_tiles[w])[h * Dh + d]; };
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * Dh; idx += 128) {
         const int h = idx / Dh, d = idx - h * Dh;
@@ -191,7 +318,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
         for (int w = 0; w < 4; ++w) {
             const float c = __expf(s_m[w][h] - mm);
             ll += s_l[w][h] * c;
-            oo += s_o[w][h][d] * c;
+            oo += s_o(w, h, d) * c;
         }
         float* dst = ws + (((int64_t)b * Hq + hk * G + h) * nsplit + sp) * (Dh + 2);
         dst[d] = oo;
@@ -245,13 +372,20 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
         const float2 rc = __bfloat1622float2(__floats2bfloat162_rn(c.x * cs[1] - c.y * sn[1], c.x * sn[1] + c.y * cs[1]));
         r[0] = ra.x; r[1] = ra.y; r[2] = rc.x; r[3] = rc.y;
     };
-    float qv[G][4];
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-        rotate(row + (hk * G + h) * Dh, qv[h]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) qv[h][e] *= scale;
+    // per warp: two buffers of K tile + V tile, reused for the warp's unnormalised output [G][128] fp32
+    extern __shared__ __align__(128) uint8_t at_smem[];
+    uint8_t (*s_tiles)[AT_WARP_BYTES] = reinterpret_cast<uint8_t (*)[AT_WARP_BYTES]>(at_smem);
+    bf16* const s_q = reinterpret_cast<bf16*>(at_smem + 4 * AT_WARP_BYTES);
+    float (*s_m)[8] = reinterpret_cast<float (*)[8]>(at_smem + 4 * AT_WARP_BYTES + 2048);
+    float (*s_l)[8] = s_m + 4;
+    int& s_last = *reinterpret_cast<int*>(at_smem + 4 * AT_WARP_BYTES + 2048 + 256);
+    for (int h = warp; h < G; h += 4) {         // rotated queries of the group, as the A operand's source
+        float r[4];
+        rotate(row + (hk * G + h) * Dh, r);
+        *reinterpret_cast<__nv_bfloat162*>(s_q + h * Dh + lane * 4) = __floats2bfloat162_rn(r[0], r[1]);
+        *reinterpret_cast<__nv_bfloat162*>(s_q + h * Dh + lane * 4 + 2) = __floats2bfloat162_rn(r[2], r[3]);
     }
+    __syncthreads();
     const bool owner = pos >= s_begin && pos < s_end;
     float knew[4] = {0, 0, 0, 0}, vnew[4] = {0, 0, 0, 0};
     bf16* kb = k_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
@@ -269,71 +403,9 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
             *reinterpret_cast<uint2*>(vb + (int64_t)pos * Dh + lane * 4) = vr;
         }
     }
-    float m[G], l[G], o[G][4];
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-        m[h] = -FLT_MAX; l[h] = 0.0f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) o[h][e] = 0.0f;
-    }
-    // positions of this warp: s_begin + warp, +4, ...; U of them are fetched before any is used so
-    // the cache reads of a batch overlap (the loop is latency bound otherwise)
-    constexpr int U = 8;
-    for (int s0 = s_begin + warp; s0 < s_end; s0 += 4 * U) {
-        uint2 kr[U], vr[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int s = s0 + 4 * u;
-            kr[u] = make_uint2(0u, 0u);
-            vr[u] = make_uint2(0u, 0u);
-            if (s < s_end && s != pos) {
-                kr[u] = __ldcg(reinterpret_cast<const uint2*>(kb + (int64_t)s * Dh + lane * 4));
-                vr[u] = __ldcg(reinterpret_cast<const uint2*>(vb + (int64_t)s * Dh + lane * 4));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int s = s0 + 4 * u;
-            if (s >= s_end) break;
-            float kf[4], vf[4];
-            if (s == pos) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) { kf[e] = knew[e]; vf[e] = vnew[e]; }
-            } else {
-                const float2 k0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[u].x));
-                const float2 k1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kr[u].y));
-                const float2 v0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr[u].x));
-                const float2 v1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vr[u].y));
-                kf[0] = k0.x; kf[1] = k0.y; kf[2] = k1.x; kf[3] = k1.y;
-                vf[0] = v0.x; vf[1] = v0.y; vf[2] = v1.x; vf[3] = v1.y;
-            }
-            float sc[G];
-#pragma unroll
-            for (int h = 0; h < G; ++h) sc[h] = qv[h][0] * kf[0] + qv[h][1] * kf[1] + qv[h][2] * kf[2] + qv[h][3] * kf[3];
-#pragma unroll
-            for (int o2 = 16; o2 > 0; o2 >>= 1)
-#pragma unroll
-                for (int h = 0; h < G; ++h) sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], o2);
-#pragma unroll
-            for (int h = 0; h < G; ++h) {
-                const float mn = fmaxf(m[h], sc[h]);
-                const float corr = __expf(m[h] - mn);
-                const float pw = __expf(sc[h] - mn);
-                l[h] = l[h] * corr + pw;
-#pragma unroll
-                for (int e = 0; e < 4; ++e) o[h][e] = o[h][e] * corr + pw * vf[e];
-                m[h] = mn;
-            }
-        }
-    }
-    __shared__ float s_m[4][G], s_l[4][G], s_o[4][G][Dh];
-    __shared__ int s_last;
-#pragma unroll
-    for (int h = 0; h < G; ++h) {
-        if (lane == 0) { s_m[warp][h] = m[h]; s_l[warp][h] = l[h]; }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s_o[warp][h][lane * 4 + e] = o[h][e];
-    }
+    attend_range<G>(kb, vb, s_begin, s_end, owner ? pos : -1, knew, vnew, s_q, scale, s_tiles[warp], s_m[warp], s_l[warp],
+                    reinterpret_cast<float*>(s_tiles[warp]), warp, lane);
+    auto s_o = [&](int w, int h, int d) -> float { return reinterpret_cast<const float*>(s_tiles[w])[h * Dh + d]; };
     __syncthreads();
     for (int idx = threadIdx.x; idx < G * Dh; idx += 128) {
         const int h = idx / Dh, d = idx - h * Dh;
@@ -345,7 +417,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
         for (int w = 0; w < 4; ++w) {
             const float c = __expf(s_m[w][h] - mm);
             ll += s_l[w][h] * c;
-            oo += s_o[w][h][d] * c;
+            oo += s_o(w, h, d) * c;
         }
         float* dst = ws + (((int64_t)b * Hq + hk * G + h) * nsplit + sp) * (Dh + 2);
         dst[d] = oo;
@@ -470,6 +542,22 @@ extern "C" int64_t nf4_b200_attn_decode_workspace_bytes(int64_t B, int Hq, int n
     return B * Hq * (int64_t)nsplit * (128 + 2) * 4;
 }
 
+// the attention kernels need more dynamic shared memory than the default limit: opt in once per device
+static int attn_configure() {
+    static bool configured[64] = {false};
+    int dev = 0;
+    NF4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 64 || configured[dev]) return NF4_OK;
+#define NF4_AT_OPT_IN(K) NF4_CUDA_TRY(cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES))
+    NF4_AT_OPT_IN(attn_decode_kernel<1>); NF4_AT_OPT_IN(attn_decode_kernel<2>);
+    NF4_AT_OPT_IN(attn_decode_kernel<4>); NF4_AT_OPT_IN(attn_decode_kernel<8>);
+    NF4_AT_OPT_IN(attn_fused_kernel<1>); NF4_AT_OPT_IN(attn_fused_kernel<2>);
+    NF4_AT_OPT_IN(attn_fused_kernel<4>); NF4_AT_OPT_IN(attn_fused_kernel<8>);
+#undef NF4_AT_OPT_IN
+    configured[dev] = true;
+    return NF4_OK;
+}
+
 static int attn_decode_launch(const void* q, const void* k_cache, const void* v_cache, const int* positions, void* out,
                               void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit,
                               void* stream) {
@@ -478,6 +566,7 @@ static int attn_decode_launch(const void* q, const void* k_cache, const void* v_
     NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 32, NF4_ERR_ARG, "attn_decode: bad geometry (1 <= nsplit <= 32)");
     if (B == 0) return NF4_OK;
     const int G = Hq / Hkv;
+    if (int rc = attn_configure()) return rc;
     dim3 grid((unsigned)Hkv, (unsigned)B, (unsigned)nsplit);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const float scale = 1.0f / sqrtf((float)Dh);
@@ -486,10 +575,10 @@ static int attn_decode_launch(const void* q, const void* k_cache, const void* v_
     const bf16* vv = static_cast<const bf16*>(v_cache);
     float* ws = static_cast<float*>(workspace);
     switch (G) {
-        case 1: attn_decode_kernel<1><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
-        case 2: attn_decode_kernel<2><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
-        case 4: attn_decode_kernel<4><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
-        case 8: attn_decode_kernel<8><<<grid, 128, 0, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        case 1: attn_decode_kernel<1><<<grid, 128, AT_SMEM_BYTES, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        case 2: attn_decode_kernel<2><<<grid, 128, AT_SMEM_BYTES, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        case 4: attn_decode_kernel<4><<<grid, 128, AT_SMEM_BYTES, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
+        case 8: attn_decode_kernel<8><<<grid, 128, AT_SMEM_BYTES, s>>>(qq, kk, vv, positions, ws, Hq, Hkv, (int)S_max, nsplit, scale); break;
         default:
             set_error("attn_decode: %d query heads per KV head (supported: 1, 2, 4, 8)", G);
             return NF4_ERR_ARG;
@@ -559,7 +648,8 @@ extern "C" int nf4_b200_attn_decode_fused(const void* qkv, const int* positions,
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)Hkv, (unsigned)B, (unsigned)nsplit);
     cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = 0;
+    if (int rc = attn_configure()) return rc;
+    cfg.dynamicSmemBytes = AT_SMEM_BYTES;
     cfg.stream = static_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
