@@ -275,9 +275,10 @@ __device__ __forceinline__ void attend_range(const bf16* __restrict__ kb, const 
 }
 
 // ---- single-query attention over the cache, split along the sequence --------------------------
-// One CTA per (kv head, batch row, split).  Dh = 128: a lane owns 4 dims.  G = Hq/Hkv query heads
-// share the K/V stream.  Partial results (max, sum, unnormalised output) go to `ws`
-// [B][Hq][nsplit][Dh + 2] fp32; attn_combine_kernel merges the splits.
+// One CTA (4 warps) per (kv head, batch row, split); Dh = 128.  The G = Hq/Hkv query heads of the group
+// share the K/V stream: each warp runs attend_range over every 4th tile of the split, the 4 warps'
+// (max, sum, unnormalised output) are merged in shared memory, and the split's partial result goes
+// to `ws` [B][Hq][nsplit][Dh + 2] fp32; attn_combine_kernel merges the splits.
 template <int G>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache,
                                                           const bf16* __restrict__ v_cache,
