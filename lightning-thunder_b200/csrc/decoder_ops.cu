@@ -349,7 +349,6 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
                                                          int nsplit, float scale, float theta) {
     constexpr int Dh = 128;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
     const int pos = positions[b];
     const int len = pos + 1;
@@ -366,6 +365,8 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
         const float inv_freq = powf(theta, -2.0f * (float)(2 * lane + j) / (float)Dh);
         sincosf((float)pos * inv_freq, &sn[j], &cs[j]);
     }
+    // positions and the rotation angles do not come from the predecessor grid (the QKV projection); qkv does
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     auto rotate = [&](const bf16* src, float (&r)[4]) {
         const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + lane * 4));
         const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + lane * 4 + 2));
@@ -487,9 +488,23 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const bf16* __restrict__ l
     const bf16* row = logits + (int64_t)blockIdx.x * V;
     float best = -FLT_MAX;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += 1024) {
-        const float v = __bfloat162float(row[i]);
-        if (v > best) { best = v; bi = i; }
+    if ((V & 7) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        // 8 logits per 16-byte load; a thread's indices still increase, so "first maximum" is kept by '>'
+        for (int i8 = threadIdx.x; i8 < V / 8; i8 += 1024) {
+            const uint4 u = *reinterpret_cast<const uint4*>(row + (int64_t)i8 * 8);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                if (f.x > best) { best = f.x; bi = i8 * 8 + 2 * j; }
+                if (f.y > best) { best = f.y; bi = i8 * 8 + 2 * j + 1; }
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += 1024) {
+            const float v = __bfloat162float(row[i]);
+            if (v > best) { best = v; bi = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

@@ -207,6 +207,16 @@ def test_glue_kernels_against_torch():
     # first maximum wins
     want = torch.stack([(row == row.max()).nonzero()[0, 0] for row in logits.float()])
     assert torch.equal(ids, want)
+    # planted ties inside one 16-byte load and across threads (vector path), and a width the vector path refuses
+    logits[0, 1000:1008] = 50.0
+    logits[1, 77] = logits[1, 77 + 8 * 1024] = 60.0
+    _lib.check(lib.nf4_b200_argmax(logits.data_ptr(), ids.data_ptr(), 4, 128256, st), "argmax")
+    assert ids[0].item() == 1000 and ids[1].item() == 77
+    odd = torch.randn((3, 1001), device="cuda", generator=g).to(torch.bfloat16)
+    odd[2, 400] = odd[2, 900] = 70.0
+    ids3 = torch.empty((3,), device="cuda", dtype=torch.int64)
+    _lib.check(lib.nf4_b200_argmax(odd.data_ptr(), ids3.data_ptr(), 3, 1001, st), "argmax")
+    assert torch.equal(ids3, torch.stack([(row == row.max()).nonzero()[0, 0] for row in odd.float()]))
     a = torch.randn((4096,), device="cuda", generator=g).to(torch.bfloat16)
     b = torch.randn((4096,), device="cuda", generator=g).to(torch.bfloat16)
     c = torch.empty_like(a)

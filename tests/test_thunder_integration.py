@@ -305,3 +305,26 @@ def test_materialization_routes_gpu():
         assert torch.equal(jm2.get_parameter(n), p), n
         assert jm.get_parameter(n).device.type == "cuda"
     torch.testing.assert_close(expected.float(), ref(x).float(), atol=2e-1, rtol=2e-1)
+
+
+@pytest.mark.gpu
+def test_cuda_graph_transform_gpu():
+    """The quantized linears inside Thunder's CUDA-graph transform (thunder/transforms/cudagraph.py:229-387,
+    what the reduce-overhead plugin installs): the op allocates nothing but its output, launches on the
+    current stream and keeps no per-call host state, so regions containing it capture and replay.  One row
+    (fused GEMV) and 40 rows (tensor-core GEMM) of activations."""
+    from thunder.transforms.cudagraph import CUDAGraphTransform
+
+    ex = get_nf4_executor()
+    m = _mlp(torch.bfloat16, "cuda")
+    jm_plain = thunder.jit(m, transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    jm_graph = thunder.jit(m, transforms=[NF4LinearQuant4bit(), CUDAGraphTransform()], executors=(ex,))
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for rows in (1, 40):
+        for _ in range(3):      # first call captures, later calls replay with new input values
+            x = torch.randn(rows, 512, device="cuda", dtype=torch.bfloat16, generator=g)
+            torch.testing.assert_close(jm_graph(x), jm_plain(x), rtol=1.6e-2, atol=1e-2)
+    trc = thunder.last_traces(jm_graph)[-1]
+    assert any("CUDAGraph" in b.sym.name for b in trc.bound_symbols), [b.sym.name for b in trc.bound_symbols]
+    from nf4_b200 import _lib
+    assert _lib.device_error()[0] == 0
