@@ -67,7 +67,6 @@ int nf4_b200_dequantize(const uint8_t* packed, const float* absmax, const float*
  * bias=, quant_state=) as called by bnb_matmul_nf4_impl (thunder/transforms/quantization.py:34-39).
  *   x, y, bias  of `dtype` (x row stride = K, y row stride = N); bias may be NULL
  *   workspace   device scratch of at least nf4_b200_linear_workspace_bytes(M, N, K, dtype) bytes
- *               (may be NULL when that is 0)
  *               (may be NULL when that is 0).  It must be zero-filled once before its first use; every
  *               call leaves it ready for the next one.  One workspace serves one stream at a time.
  *               Without it the result is the same sums computed by fewer thread blocks.
