@@ -108,16 +108,22 @@ __global__ void __launch_bounds__(QTHREADS) quantize_kernel(const T* __restrict_
     const int64_t stride = (int64_t)gridDim.x * QTHREADS;
     // all threads of a CTA iterate the same number of times (shared-memory max needs barriers)
     const int64_t niter = (ngroups8 + stride - 1) / stride;
+    // the load of the next iteration is issued before this iteration's arithmetic (the kernel is bound by
+    // instruction issue; this keeps twice the bytes in flight)
+    float vn[8];
+    {
+        const int64_t t0 = (int64_t)blockIdx.x * QTHREADS + threadIdx.x;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vn[i] = 0.0f;
+        if (t0 < ngroups8) load8<T>(w + t0 * 8, vn);
+    }
     for (int64_t it = 0; it < niter; ++it) {
         const int64_t t = it * stride + (int64_t)blockIdx.x * QTHREADS + threadIdx.x;
         const bool live = t < ngroups8;
         float v[8];
-        if (live) {
-            load8<T>(w + t * 8, v);
-        } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.0f;
-        }
+        for (int i = 0; i < 8; ++i) { v[i] = vn[i]; vn[i] = 0.0f; }
+        if (t + stride < ngroups8) load8<T>(w + (t + stride) * 8, vn);
         float am = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) am = fmaxf(am, fabsf(v[i]));
@@ -142,15 +148,25 @@ __global__ void __launch_bounds__(QTHREADS) quantize_kernel(const T* __restrict_
             // Scales outside [2^-100, 2^100] take the compiler's fully guarded division.
             const float dv = am == 0.0f ? 1.0f : am;
             const bool bounded = dv >= 7.8886e-31f && dv <= 1.2676e30f;
-            const float rcp = refined_rcp(dv);
+            // the two choices below are uniform per block / per CTA: they select one of three straight-line
+            // loops instead of being re-decided for every element
+            if (bounded && bucketed) {
+                const float rcp = refined_rcp(dv);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float qv = bounded ? div_rn_bounded(v[i], dv, rcp) : __fdiv_rn(v[i], dv);
-                uint32_t idx = bucketed ? nf4_index_bucketed(qv, s_bt) : nf4_index(qv, s_thr);
-                // element 2j -> high nibble of byte j; bytes are little-endian inside the word
-                const int byte = i >> 1;
-                const int shift = byte * 8 + ((i & 1) ? 0 : 4);
-                word |= idx << shift;
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t idx = nf4_index_bucketed(div_rn_bounded(v[i], dv, rcp), s_bt);
+                    // element 2j -> high nibble of byte j; bytes are little-endian inside the word
+                    word |= idx << ((i >> 1) * 8 + ((i & 1) ? 0 : 4));
+                }
+            } else if (bounded) {
+                const float rcp = refined_rcp(dv);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    word |= nf4_index(div_rn_bounded(v[i], dv, rcp), s_thr) << ((i >> 1) * 8 + ((i & 1) ? 0 : 4));
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    word |= nf4_index(__fdiv_rn(v[i], dv), s_thr) << ((i >> 1) * 8 + ((i & 1) ? 0 : 4));
             }
             packed32[t] = word;
             if ((t & (GROUP - 1)) == 0) absmax[t / GROUP] = am;
