@@ -599,15 +599,23 @@ static int gemm_layout(int TM, GemmParams* p) {
 constexpr int64_t GM_COUNTER_BYTES = 4096;   // head of the split-K workspace: arrival counters
 
 // Tile height and K split for a shape.  Few weight tiles (decode shapes, narrow layers) leave SMs idle, so K
-// is cut into ranges until about one CTA per SM exists; each range keeps >= 4 K blocks.
+// is cut into ranges until about one CTA per SM exists.
 static void gemm_plan(int64_t M, int64_t N, int64_t K, int* TM_out, int* splits_out) {
     int TM = 256;
     while (TM > 32 && TM / 2 >= M) TM /= 2;         // 32, 64, 128 or 256 activation rows per CTA
+    if (const char* e = getenv("NF4_GEMM_TM")) {     // tuning override
+        const int v = atoi(e);
+        if ((v == 32 || v == 64 || v == 128 || v == 256) && v <= TM) TM = v;
+    }
     const int64_t ctas = ((N + GM_BM - 1) / GM_BM) * ((M + TM - 1) / TM);
     int64_t splits = GM_SM_TARGET / ctas;            // one CTA per SM is resident
     const int64_t KB = K / 64;
     const int64_t max_splits = KB % GM_WKB == 0 ? KB / GM_WKB : KB;    // ranges are whole groups when they can be
-    if (splits > KB / 4) splits = KB / 4;
+    // a range keeps at least 4 K blocks; 48 for tall tiles, whose fp32 partial sums (TM x 128 x 4 bytes per
+    // split) cost as much as dozens of K blocks (measured: 4096x4096, M=256 loses 40 % with 16-block ranges,
+    // 4096x14336 gains 50 % with 56-block ranges)
+    const int64_t min_kb = TM > 64 ? 48 : 4;
+    if (splits > KB / min_kb) splits = KB / min_kb;
     if (splits < 1) splits = 1;
     const char* e = getenv("NF4_GEMM_SPLITS");
     const int forced = e ? atoi(e) : -1;
