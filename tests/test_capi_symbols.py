@@ -62,3 +62,28 @@ def test_functional_refuses_cpu_tensors():
 
     with pytest.raises(RuntimeError, match="CUDA"):
         nf4_b200.quantize_4bit(torch.zeros(64, dtype=torch.bfloat16))
+
+
+def test_tensor_core_entry_points_validate_arguments_without_a_gpu():
+    """Argument checks come before any device call, so they can be exercised on a CPU-only machine."""
+    import ctypes
+
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    p = ctypes.c_void_p(256)
+    rc = lib.nf4_b200_gemm_decode(p, 16, 128, p, p, p, 7, None, p, 1, None, 0, 0, None)
+    assert rc == 1 and "epilogue" in _lib.last_error()           # SwiGLU needs an even N
+    rc = lib.nf4_b200_gemm_decode(p, 16, 128, p, p, p, 8, p, p, 1, None, 0, 0, None)
+    assert rc == 1 and "epilogue" in _lib.last_error()           # ... and no residual
+    rc = lib.nf4_b200_gemm_decode(p, 16, 100, p, p, p, 8, None, p, 0, None, 0, 0, None)
+    assert rc == 1 and "multiple of 64" in _lib.last_error()
+    assert lib.nf4_b200_gemv_decode_next_weight(p, p, 8, 100) == 1
+    assert lib.nf4_b200_gemv_decode_next_weight(p, p, 4096, 4096) == 0
+    assert lib.nf4_b200_gemv_decode_next_weight(None, None, 0, 0) == 0      # clears the pending hint
+    # K-split planning: decode shapes with few 128-row tiles split; tall tiles only with long K ranges
+    assert lib.nf4_b200_gemm_workspace_bytes(16, 4096, 4096) > 0
+    assert lib.nf4_b200_gemm_workspace_bytes(16, 128256, 4096) == 0
+    assert lib.nf4_b200_gemm_workspace_bytes(256, 4096, 4096) == 0
+    assert lib.nf4_b200_gemm_workspace_bytes(256, 4096, 14336) > 0
+    assert lib.nf4_b200_gemm_workspace_bytes(2048, 14336, 4096) == 0
