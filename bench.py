@@ -250,6 +250,62 @@ def run_kernel(args):
     print(json.dumps(out))
 
 
+def run_attention(args):
+    """The decode step's attention launch (rotary + KV append + attention over the cache + merge of the
+    splits) by itself: one CUDA graph of one launch per layer over distinct caches (cold reads), timed with
+    events; bytes = the K and V rows read."""
+    import ctypes
+
+    import torch
+
+    from nf4_b200 import _lib
+
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    B, Hq, Hkv, ctx, Dh = args.B, args.Hq, args.Hkv, args.ctx, 128
+    S = ctx + 8
+    per_layer = B * Hkv * S * Dh * 2 * 2
+    L = args.nbuf or max(2, int(4 * 126e6 // per_layer) + 1)          # rotating caches exceed four times the L2
+    ns = args.splits or max(1, min(16, 296 // max(1, Hkv * B), S // 128))
+    g = torch.Generator(device="cuda").manual_seed(0)
+    k = torch.randn((L, B, Hkv, S, Dh), device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn((L, B, Hkv, S, Dh), device="cuda", generator=g).to(torch.bfloat16)
+    qkv = torch.randn((B, (Hq + 2 * Hkv) * Dh), device="cuda", generator=g).to(torch.bfloat16)
+    out = torch.empty((B, Hq * Dh), device="cuda", dtype=torch.bfloat16)
+    pos = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    cnt = torch.zeros((B * Hkv,), device="cuda", dtype=torch.int32)
+    ws = torch.empty((lib.nf4_b200_attn_decode_workspace_bytes(B, Hq, ns),), device="cuda", dtype=torch.uint8)
+
+    def launch_all():
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        for l in range(L):
+            _lib.check(lib.nf4_b200_attn_decode_fused(qkv.data_ptr(), pos.data_ptr(), k[l].data_ptr(), v[l].data_ptr(), out.data_ptr(),
+                                                      ws.data_ptr(), cnt.data_ptr(), B, Hq, Hkv, Dh, S, ns, 500000.0, 0, st), "attention")
+
+    for _ in range(max(1, args.warmup)):
+        launch_all()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        launch_all()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ts = []
+    for _ in range(max(1, args.steps)):
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / L)
+    us = statistics.median(ts)
+    alg = B * Hkv * (ctx + 1) * Dh * 2 * 2
+    peaks, src = measured_peaks()
+    print(json.dumps({"kernel": "attention", "B": B, "Hq": Hq, "Hkv": Hkv, "ctx": ctx, "splits": ns, "us_per_launch": us,
+                      "algorithmic_bytes": alg, "GBps": alg / us / 1e3, "hbm_frac_of_" + src: alg / us / 1e3 / peaks["hbm_gbs"],
+                      "buffers": L, "device_error": list(_lib.device_error())}))
+
+
 # --------------------------------------------------------------------------------------------
 # the decode benchmark
 # --------------------------------------------------------------------------------------------
@@ -449,7 +505,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "llama3-8b", "llama3-70b", "tiny"])
     ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
-    ap.add_argument("--kernel", default=None, choices=[None, "gemv", "gemm", "quantize", "dequantize"])
+    ap.add_argument("--kernel", default=None, choices=[None, "gemv", "gemm", "quantize", "dequantize", "attention"])
+    ap.add_argument("--B", type=int, default=16, help="attention: sequences")
+    ap.add_argument("--Hq", type=int, default=64, help="attention: query heads")
+    ap.add_argument("--Hkv", type=int, default=8, help="attention: key/value heads")
+    ap.add_argument("--ctx", type=int, default=1024, help="attention: cached positions per sequence")
+    ap.add_argument("--splits", type=int, default=0, help="attention: splits along the sequence (0: the decoder's rule)")
     ap.add_argument("--N", type=int, default=14336)
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--M", type=int, default=1)
@@ -457,6 +518,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.kernel == "attention":
+        run_attention(args)
     elif args.kernel:
         run_kernel(args)
     else:
