@@ -153,8 +153,10 @@ int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const uint8_t* pac
  * Optional hint for the NEXT nf4_b200_gemv_decode call made by this host thread (that call consumes it):
  * the weight (packed, absmax, N, K) of the launch that will follow it on the same stream.  Each thread
  * block of the hinted call pulls the head of its share of that weight into L2 once its own loads are in
- * flight, which keeps HBM busy across the kernel boundary.  Purely a prefetch: results do not change,
- * a wrong hint only wastes bandwidth.  NULL pointers clear a pending hint.  No counterpart in the reference.
+ * flight, which keeps HBM busy across the kernel boundary.  Purely a prefetch: results do not change, and
+ * a hint for a weight that is not read next only wastes bandwidth -- but the hinted buffers must be live
+ * device memory of those extents when the hinted call runs (the prefetch touches them).  NULL pointers
+ * clear a pending hint.  No counterpart in the reference.
  */
 int nf4_b200_gemv_decode_next_weight(const uint8_t* packed, const float* absmax, int64_t N, int64_t K);
 
