@@ -267,3 +267,114 @@ def linear_nf4_dq(x: torch.Tensor, packed: torch.Tensor, bias, state: QuantState
             "nf4_b200_linear_dq",
         )
     return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# Decode-step forms (one launch each).  The reference has no fused form of these: they fold the ops
+# between two quantized linears of a Llama-shaped block (thunder/tests/llama2_model.py:142-190) into
+# the linear.  The Thunder executor's block symbols (nf4_b200.fusion) are written in terms of these
+# three functions and look them up at call time, so CPU tests can substitute checkers for them.
+# ---------------------------------------------------------------------------------------------------
+
+PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_SWIGLU = 0, 1, 2
+EPILOGUE_NONE, EPILOGUE_SWIGLU_INTERLEAVED, EPILOGUE_SWIGLU_HALVES = 0, 1, 2
+
+
+def gemv_decode_fits(M: int, N: int, K: int, prologue: int) -> bool:
+    return bool(_lib.load().nf4_b200_gemv_decode_fits(int(M), int(N), int(K), int(prologue)))
+
+
+def gemv_decode(x: torch.Tensor, packed: torch.Tensor, absmax: torch.Tensor, code: torch.Tensor, N: int, K: int, *,
+                prologue: int = 0, norm_w=None, eps: float = 0.0, epilogue: int = 0, residual=None, out=None,
+                pdl: bool = False) -> torch.Tensor:
+    """y = prologue(x) @ dequant(W[N, K]).T (+ residual), bf16, at most 16 activation rows.
+    prologue 1: RMSNorm of x with weight norm_w; 2: x is [M, 2K] = [gate | up] and becomes silu(gate) * up.
+    epilogue 1 / 2: W's rows are (gate_i, up_i) pairs / W is [gate rows; up rows], and y [M, N/2] =
+    silu(x.gate_i) * (x.up_i)."""
+    _require_cuda(x, "gemv_decode input")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("gemv_decode: bf16 activations only")
+    in_cols = 2 * K if prologue == PROLOGUE_SWIGLU else K
+    if x.shape[-1] != in_cols:
+        raise RuntimeError(f"gemv_decode: x.shape={tuple(x.shape)} does not match K={K} (prologue {prologue})")
+    x2 = x.reshape(-1, in_cols)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    n_out = N // 2 if epilogue else N
+    with torch.cuda.device(x.device):
+        if out is None:
+            out = torch.empty((*x.shape[:-1], n_out), dtype=x.dtype, device=x.device)
+        _lib.check(
+            _lib.load().nf4_b200_gemv_decode(x2.data_ptr(), M, K, packed.data_ptr(), absmax.data_ptr(), code.data_ptr(), N,
+                                             residual.data_ptr() if residual is not None else None, out.data_ptr(),
+                                             int(prologue), norm_w.data_ptr() if norm_w is not None else None, float(eps),
+                                             int(epilogue), 1 if pdl else 0, _stream_ptr(x.device)),
+            "nf4_b200_gemv_decode",
+        )
+    return out
+
+
+_ATTN_SCRATCH: dict = {}
+
+
+def attn_splits(B: int, Hkv: int, S_max: int) -> int:
+    """Splits along the cached sequence: enough thread blocks (kv heads x sequences x splits) to cover
+    the SMs about twice, but at least ~128 cached positions per block."""
+    return max(1, min(16, 296 // max(1, Hkv * B), S_max // 128))
+
+
+def attn_decode_fused(qkv: torch.Tensor, positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      Hq: int, Hkv: int, theta: float, *, pdl: bool = False, out=None) -> torch.Tensor:
+    """Single-query attention of a decode step in one launch: rotates q and the new k (interleaved
+    pairs, base theta) at positions[b], writes k and v into the caches [B, Hkv, S_max, 128] at that
+    row and attends over rows 0..positions[b].  qkv [B, (Hq + 2 Hkv) * 128] bf16, positions int32 [B].
+    Returns [B, Hq * 128].  The caches are updated in place."""
+    _require_cuda(qkv, "attn_decode_fused input")
+    B = qkv.shape[0]
+    Dh = 128
+    S_max = k_cache.shape[2]
+    if qkv.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise ValueError("attn_decode_fused: bf16 tensors only")
+    if positions.dtype != torch.int32 or positions.numel() != B:
+        raise ValueError("attn_decode_fused: positions must be int32 [B]")
+    if tuple(k_cache.shape[1:]) != (Hkv, S_max, Dh) or k_cache.shape != v_cache.shape or k_cache.shape[0] < B:
+        raise RuntimeError(f"attn_decode_fused: cache shape {tuple(k_cache.shape)} does not fit B={B}, Hkv={Hkv}")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous() and qkv.is_contiguous()):
+        raise RuntimeError("attn_decode_fused: qkv and the caches must be contiguous")
+    lib = _lib.load()
+    ns = attn_splits(B, Hkv, S_max)
+    key = (qkv.device.index, B, Hq, Hkv, ns)
+    scratch = _ATTN_SCRATCH.get(key)
+    with torch.cuda.device(qkv.device):
+        if scratch is None:
+            # kept for the life of the process (a captured CUDA graph holds these addresses)
+            ws = torch.empty((lib.nf4_b200_attn_decode_workspace_bytes(B, Hq, ns),), dtype=torch.uint8, device=qkv.device)
+            counters = torch.zeros((B * Hkv,), dtype=torch.int32, device=qkv.device)
+            scratch = _ATTN_SCRATCH[key] = (ws, counters)
+        ws, counters = scratch
+        if out is None:
+            out = torch.empty((B, Hq * Dh), dtype=qkv.dtype, device=qkv.device)
+        _lib.check(
+            lib.nf4_b200_attn_decode_fused(qkv.data_ptr(), positions.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                           out.data_ptr(), ws.data_ptr(), counters.data_ptr(), B, Hq, Hkv, Dh, S_max, ns,
+                                           float(theta), 1 if pdl else 0, _stream_ptr(qkv.device)),
+            "nf4_b200_attn_decode_fused",
+        )
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, F: int, interleaved: bool) -> torch.Tensor:
+    """[rows, 2F] -> [rows, F]: silu(gate) * up with gate/up as halves or as interleaved pairs."""
+    _require_cuda(gate_up, "silu_mul input")
+    g2 = gate_up.reshape(-1, 2 * F)
+    with torch.cuda.device(gate_up.device):
+        out = torch.empty((*gate_up.shape[:-1], F), dtype=gate_up.dtype, device=gate_up.device)
+        _lib.check(_lib.load().nf4_b200_silu_mul(g2.data_ptr(), out.data_ptr(), g2.shape[0], F, 1 if interleaved else 0,
+                                                 _stream_ptr(gate_up.device)), "nf4_b200_silu_mul")
+    return out
+
+
+def swiglu_halves_available() -> bool:
+    """Whether the fused GEMV has the SwiGLU epilogue over [gate rows; up rows] (epilogue 2)."""
+    return _lib.HAS_SWIGLU_HALVES

@@ -1,0 +1,174 @@
+"""The decode-step fusion pass (nf4_b200.fusion.NF4DecodeFusion) on the Llama-shaped module with a KV
+cache (nf4_b200.llama): which symbols the rewritten trace holds, that parameters keep their names, shapes
+and values, and that a fused and an unfused jitted copy of the same model decode the same logits.
+
+CPU tests run the block symbols on CPU checkers (oracle for the quantized products, torch for the glue);
+GPU tests run them on the kernels and compare with the oracle-backed unfused module."""
+
+import pytest
+import torch
+
+from helpers import cpu_attn_decode_fused, cpu_gemv_decode, cpu_silu_mul
+from test_thunder_integration import _oracle_linear_nf4, _oracle_quantize_4bit
+
+thunder_support = pytest.importorskip("nf4_b200.thunder_support")
+if not thunder_support.thunder_available():
+    pytest.skip("thunder is not importable (no baseline/_ref)", allow_module_level=True)
+
+import thunder  # noqa: E402
+
+from nf4_b200 import functional  # noqa: E402
+from nf4_b200.fusion import NF4DecodeFusion  # noqa: E402
+from nf4_b200.llama import LlamaArgs, LlamaDecoder  # noqa: E402
+from nf4_b200.thunder_executor import NF4LinearQuant4bit, get_nf4_executor  # noqa: E402
+
+
+@pytest.fixture
+def cpu_backend(monkeypatch):
+    monkeypatch.setattr(functional, "quantize_4bit", _oracle_quantize_4bit)
+    monkeypatch.setattr(functional, "linear_nf4", _oracle_linear_nf4)
+    monkeypatch.setattr(functional, "gemv_decode", cpu_gemv_decode)
+    monkeypatch.setattr(functional, "gemv_decode_fits", lambda M, N, K, prologue: True)
+    monkeypatch.setattr(functional, "attn_decode_fused", cpu_attn_decode_fused)
+    monkeypatch.setattr(functional, "silu_mul", cpu_silu_mul)
+    monkeypatch.setattr(functional, "swiglu_halves_available", lambda: True)
+    monkeypatch.setattr(NF4LinearQuant4bit, "quantize_weight", lambda self, w: functional.quantize_4bit(w, quant_type="nf4"))
+
+
+def tiny_args(**kw):
+    base = dict(dim=256, n_layers=2, n_heads=2, n_kv_heads=1, vocab_size=512, hidden_dim=512, max_seq_len=32, max_batch=2)
+    base.update(kw)
+    return LlamaArgs(**base)
+
+
+def build(args, device="cpu", seed=1):
+    m = LlamaDecoder(args).to(device=device, dtype=torch.bfloat16).eval().requires_grad_(False)
+    m.init_weights(seed)
+    m.reset_rope_tables()
+    return m
+
+
+def _names(trc):
+    return [b.sym.name for b in trc.bound_symbols]
+
+
+def _decode(jm, steps, B, vocab, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    dev = next(iter(jm.state_dict().values())).device
+    outs = []
+    for p in range(steps):
+        tok = torch.randint(0, vocab, (B, 1), generator=g).to(dev)
+        outs.append(jm(tok, torch.tensor([p], device=dev)).float().cpu())
+    return torch.stack(outs)
+
+
+def test_trace_is_rewritten_and_matches_unfused_cpu(cpu_backend):
+    args = tiny_args()
+    ex = get_nf4_executor()
+    fusion = NF4DecodeFusion()
+    jf = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), fusion], executors=(ex,))
+    ju = thunder.jit(build(args), transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    got = _decode(jf, 5, 2, args.vocab_size)
+    want = _decode(ju, 5, 2, args.vocab_size)
+    names = _names(thunder.last_traces(jf)[-1])
+    assert names.count("nf4_b200_attn_block") == args.n_layers
+    assert names.count("nf4_b200_mlp_block") == args.n_layers
+    assert names.count("nf4_b200_norm_linear") == 1
+    assert names.count("nf4_b200_positions") == 1
+    assert "nf4_b200_matmul" not in names and "scaled_dot_product_attention" not in names
+    assert not any(n in names for n in ("index_copy_", "index_copy", "rms_norm", "silu")), names
+    assert fusion.fused == {"attn": 2, "mlp": 2, "norm_linear": 1} and not fusion.declined
+    assert "NF4 decode fusion" in str([t.get_provenance() for t in thunder.last_traces(jf)])
+    torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1e-2)
+    # the caches were written in place by the fused block, exactly where the unfused module wrote them
+    for li in range(args.n_layers):
+        kf = jf.get_buffer(f"layers.{li}.attention.k_cache")
+        ku = ju.get_buffer(f"layers.{li}.attention.k_cache")
+        assert kf[:, :, 5:].abs().max() == 0 and kf[:, :, :5].abs().max() > 0
+        torch.testing.assert_close(kf.float(), ku.float(), rtol=1.6e-2, atol=1e-2)
+
+
+def test_parameters_keep_names_shapes_and_values_cpu(cpu_backend):
+    """Q/K/V and gate/up become views into one allocation each; the state dict is unchanged and loading the
+    original weights again (thunder/core/module.py:137-190 copies in place) keeps them adjacent."""
+    args = tiny_args()
+    ex = get_nf4_executor()
+    model = build(args)
+    jf = thunder.jit(model, transforms=[NF4LinearQuant4bit(), NF4DecodeFusion()], executors=(ex,))
+    ju = thunder.jit(build(args), transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    _decode(jf, 1, 2, args.vocab_size)
+    sf, su = jf.state_dict(), ju.state_dict()
+    assert list(sf) == list(su)
+    for k in su:
+        assert sf[k].shape == su[k].shape and sf[k].dtype == su[k].dtype and torch.equal(sf[k], su[k]), k
+    p = "layers.0.attention."
+    wq, wk, wv = (jf.get_parameter(p + n + ".weight") for n in ("wq", "wk", "wv"))
+    assert wk.data_ptr() == wq.data_ptr() + wq.numel() and wv.data_ptr() == wk.data_ptr() + wk.numel()
+    aq, ak = jf.get_parameter(p + "wq.weight.absmax"), jf.get_parameter(p + "wk.weight.absmax")
+    assert ak.data_ptr() == aq.data_ptr() + 4 * aq.numel()
+    w1, w3 = jf.get_parameter("layers.1.feed_forward.w1.weight"), jf.get_parameter("layers.1.feed_forward.w3.weight")
+    assert w3.data_ptr() == w1.data_ptr() + w1.numel()
+    other = build(args, seed=7)
+    jf.load_original_state_dict(other.state_dict())
+    jo = thunder.jit(other, transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    assert jf.get_parameter(p + "wk.weight").data_ptr() == jf.get_parameter(p + "wq.weight").data_ptr() + wq.numel()
+    for k, v in jo.state_dict().items():
+        assert torch.equal(jf.state_dict()[k], v), k
+
+
+def test_prefill_trace_is_left_alone_cpu(cpu_backend):
+    """More than 16 activation rows: the pass declines (those linears belong to the tensor-core GEMM) and
+    says why for the attention."""
+    args = tiny_args(max_batch=1)
+    fusion = NF4DecodeFusion()
+    jf = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), fusion], executors=(get_nf4_executor(),))
+    tok = torch.randint(0, args.vocab_size, (1, 24))
+    y = jf(tok, torch.arange(24))
+    assert y.shape == (1, 1, args.vocab_size)
+    names = _names(thunder.last_traces(jf)[-1])
+    assert "nf4_b200_attn_block" not in names and "nf4_b200_mlp_block" not in names
+    assert names.count("nf4_b200_matmul") == 7 * args.n_layers       # the head's single row is still fused
+    assert names.count("nf4_b200_norm_linear") == 1
+    assert fusion.declined and "single-token" in fusion.declined[0]
+    # the same module then decodes token by token on the fused blocks (a second trace for the new shapes)
+    y1 = jf(torch.randint(0, args.vocab_size, (1, 1)), torch.tensor([24]))
+    assert y1.shape == (1, 1, args.vocab_size)
+    assert "nf4_b200_attn_block" in _names(thunder.last_traces(jf)[-1])
+
+
+def test_other_rope_base_is_declined_cpu(cpu_backend):
+    args = tiny_args()
+    fusion = NF4DecodeFusion(rope_theta=10000.0)          # the module's tables use 500000
+    jf = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), fusion], executors=(get_nf4_executor(),))
+    _decode(jf, 1, 2, args.vocab_size)
+    names = _names(thunder.last_traces(jf)[-1])
+    assert "nf4_b200_attn_block" not in names and names.count("nf4_b200_mlp_block") == args.n_layers
+    assert any("rope tables" in d for d in fusion.declined)
+
+
+# ------------------------------------------------------------------------------------------ GPU
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B", [1, 4])
+def test_fused_decode_on_kernels_matches_oracle_backend(monkeypatch, B):
+    """Jitted + fused + CUDA-graphed decode on the GPU against the unfused module on the CPU oracle."""
+    from thunder.transforms.cudagraph import CUDAGraphTransform
+
+    from nf4_b200 import _lib
+
+    args = tiny_args(dim=512, n_heads=4, n_kv_heads=2, hidden_dim=1024, vocab_size=2048, max_seq_len=64, max_batch=B)
+    ex = get_nf4_executor()
+    fusion = NF4DecodeFusion()
+    jg = thunder.jit(build(args, "cuda"), transforms=[NF4LinearQuant4bit(), fusion, CUDAGraphTransform()], executors=(ex,))
+    got = _decode(jg, 6, B, args.vocab_size)
+    assert fusion.fused["attn"] == args.n_layers and not fusion.declined
+    names = _names(thunder.last_traces(jg)[-1])
+    assert any("CUDAGraph" in n for n in names)
+    assert _lib.device_error()[0] == 0
+    monkeypatch.setattr(functional, "quantize_4bit", _oracle_quantize_4bit)
+    monkeypatch.setattr(functional, "linear_nf4", _oracle_linear_nf4)
+    monkeypatch.setattr(NF4LinearQuant4bit, "quantize_weight", lambda self, w: functional.quantize_4bit(w, quant_type="nf4"))
+    jc = thunder.jit(build(args, "cpu"), transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    want = _decode(jc, 6, B, args.vocab_size)
+    torch.testing.assert_close(got, want, rtol=5e-2, atol=5e-2)
+    assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.9
