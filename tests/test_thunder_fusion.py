@@ -42,8 +42,10 @@ def tiny_args(**kw):
 
 
 def build(args, device="cpu", seed=1):
-    m = LlamaDecoder(args).to(device=device, dtype=torch.bfloat16).eval().requires_grad_(False)
+    # weights are drawn on the CPU generator whatever the device, so a CPU and a GPU copy are the same model
+    m = LlamaDecoder(args).to(dtype=torch.bfloat16).eval().requires_grad_(False)
     m.init_weights(seed)
+    m = m.to(device)
     m.reset_rope_tables()
     return m
 
