@@ -137,7 +137,9 @@ int nf4_b200_gemv_fused(const void* x, int64_t M, int64_t K, const uint8_t* pack
  *   prologue 0: none;  1: x <- x * rsqrt(mean(x^2) + eps) * norm_w (RMSNorm, norm_w [K]);
  *   2: x is [M, 2K] = [gate | up] and x <- silu(gate) * up (SwiGLU).
  * epilogue 0: y [M, N];  1: the weight's rows are (gate_i, up_i) pairs (row 2i, row 2i+1) and
- *   y [M, N/2] = silu(x.gate_i) * (x.up_i), both sums rounded to bf16 first (no residual).
+ *   y [M, N/2] = silu(x.gate_i) * (x.up_i), both sums rounded to bf16 first (no residual);
+ *   2: the same with the weight stored as [gate rows; up rows] (row i and row N/2 + i; N % 16 == 0) --
+ *   the layout of two separately quantized matrices placed back to back in memory.
  * flags bit 0: launch with programmatic stream serialization (the kernel starts streaming weights
  * while the previous kernel of the stream is finishing and waits for it before touching x, residual
  * or y; the previous and next kernels must come from this library).  Returns NF4_ERR_LIMIT when the
@@ -174,14 +176,19 @@ int nf4_b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int64_
 int nf4_b200_rope_append(const void* qkv, const int* positions, void* q_out, void* k_cache, void* v_cache,
                          int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, float theta, void* stream);
 /* Single-query grouped attention over cache positions [0, positions[b]]; out [B, Hq*Dh].  Dh = 128.
- * workspace: nf4_b200_attn_decode_workspace_bytes(B, Hq, nsplit) bytes. */
+ * workspace: nf4_b200_attn_decode_workspace_bytes(B, Hq, nsplit) bytes.
+ * In all kernels below a positions[b] outside [0, S_max) touches no cache row: that sequence writes
+ * nothing, attends to nothing (its output is zero) and code 9 is recorded in nf4_b200_device_error. */
 int64_t nf4_b200_attn_decode_workspace_bytes(int64_t B, int Hq, int nsplit);
 int nf4_b200_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int* positions, void* out,
                          void* workspace, int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, int nsplit, void* stream);
 /* nf4_b200_rope_append + nf4_b200_attn_decode in ONE launch: reads qkv [B, (Hq+2*Hkv)*Dh], rotates q and
  * the new k at positions[B], appends k, v to the caches and attends over [0, positions[b]].  `counters`:
  * B*Hkv unsigned ints that must be zero before the first call (the kernel leaves them zero).  flags bit
- * 0: programmatic dependent launch (see nf4_b200_gemv_decode).  No counterpart in the reference. */
+ * 0: programmatic dependent launch (see nf4_b200_gemv_decode); with it the kernel reads `positions` before
+ * it waits for its predecessor, so positions must hold their final values before the PRECEDING launch on
+ * the stream starts (update them after the attention launches of a step, not between the QKV projection
+ * and the attention).  No counterpart in the reference. */
 int nf4_b200_attn_decode_fused(const void* qkv, const int* positions, void* k_cache, void* v_cache, void* out,
                                void* workspace, unsigned int* counters, int64_t B, int Hq, int Hkv, int Dh,
                                int64_t S_max, int nsplit, float theta, int flags, void* stream);
@@ -219,7 +226,8 @@ int nf4_b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t V, v
  * Status word of the kernels that wait on in-kernel barriers (the staged GEMV).  Copies 4 words to
  * host memory: [0] first error code (0 = none; GEMV: 1/2/3 = a bounded wait on a full/empty/activation
  * barrier ran out, 4 = unexpected shared-memory window; GEMM: 5/6/7/8 = a bounded wait on the
- * full/empty/weights-ready/accumulator barrier ran out), [1] block index, [2] pipeline stage,
+ * full/empty/weights-ready/accumulator barrier ran out; attention / rotary kernels: 9 = a position outside
+ * [0, S_max), then [1] is the batch row and [2] the position), [1] block index, [2] pipeline stage,
  * [3] number of waits that ran out.  SYNCHRONISES the device; for tests and diagnosis only.  No
  * counterpart in the reference.
  */

@@ -43,6 +43,23 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* __restrict__ x
     }
 }
 
+// Status word of the kernels that index the KV cache with a position read from device memory:
+// [0] first error code (9 = a position outside [0, S_max)), [1] batch row, [2] the position, [3] count.
+// Such a row writes nothing to the cache and attends to nothing (its output is zero).
+__device__ unsigned int g_attn_error[4];
+
+__device__ __forceinline__ bool position_ok(int pos, int S_max, int b) {
+    if (pos >= 0 && pos < S_max) return true;
+    if (threadIdx.x == 0) {
+        if (atomicCAS(&g_attn_error[0], 0u, 9u) == 0u) {
+            g_attn_error[1] = (unsigned)b;
+            g_attn_error[2] = (unsigned)pos;
+        }
+        atomicAdd(&g_attn_error[3], 1u);
+    }
+    return false;
+}
+
 // ---- rotary embedding on q and k (interleaved pairs) + append k, v to the cache ---------------
 // qkv [B][(Hq + 2*Hkv) * Dh] as produced by the fused QKV linear; q_out [B][Hq*Dh];
 // k_cache / v_cache [B][Hkv][S_max][Dh]; positions[B] = index of the token being written.
@@ -52,9 +69,11 @@ __global__ void rope_append_kernel(const bf16* __restrict__ qkv, const int* __re
     const int b = blockIdx.y;
     const int head = blockIdx.x;              // 0..Hq+2*Hkv-1
     const int pos = positions[b];
+    const bool pos_ok = position_ok(pos, S_max, b);
     const bf16* src = qkv + ((int64_t)b * (Hq + 2 * Hkv) + head) * Dh;
     const int i = threadIdx.x;                // pair index, Dh/2 threads
     if (i >= Dh / 2) return;
+    if (!pos_ok && head >= Hq) return;        // nothing is written outside the cache
     const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 2 * i));
     if (head < Hq + Hkv) {
         const float inv_freq = powf(theta, -2.0f * (float)i / (float)Dh);
@@ -286,7 +305,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const bf16* __restrict
                                                           int Hq, int Hkv, int S_max, int nsplit, float scale) {
     constexpr int Dh = 128;
     const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
-    const int len = positions[b] + 1;                      // attend to [0, pos]
+    const int len = position_ok(positions[b], S_max, b) ? positions[b] + 1 : 0;    // attend to [0, pos]
     const int chunk = (len + nsplit - 1) / nsplit;
     const int s_begin = sp * chunk;
     const int s_end = min(len, s_begin + chunk);
@@ -351,7 +370,8 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
     const int pos = positions[b];
-    const int len = pos + 1;
+    const bool pos_ok = position_ok(pos, S_max, b);
+    const int len = pos_ok ? pos + 1 : 0;
     const int chunk = (len + nsplit - 1) / nsplit;
     const int s_begin = sp * chunk;
     const int s_end = min(len, s_begin + chunk);
@@ -388,7 +408,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
         *reinterpret_cast<__nv_bfloat162*>(s_q + h * Dh + lane * 4 + 2) = __floats2bfloat162_rn(r[2], r[3]);
     }
     __syncthreads();
-    const bool owner = pos >= s_begin && pos < s_end;
+    const bool owner = pos_ok && pos >= s_begin && pos < s_end;
     float knew[4] = {0, 0, 0, 0}, vnew[4] = {0, 0, 0, 0};
     bf16* kb = k_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
     bf16* vb = v_cache + ((int64_t)b * Hkv + hk) * S_max * Dh;
@@ -527,6 +547,12 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const bf16* __restrict__ l
     }
 }
 
+// host side: copies the attention status word (synchronises)
+int attn_read_error(unsigned int* out4) {
+    NF4_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_attn_error, sizeof(unsigned int) * 4));
+    return NF4_OK;
+}
+
 }  // namespace nf4
 
 using namespace nf4;
@@ -545,6 +571,7 @@ extern "C" int nf4_b200_rope_append(const void* qkv, const int* positions, void*
                                     int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, float theta, void* stream) {
     NF4_REQUIRE(qkv && positions && q_out && k_cache && v_cache, NF4_ERR_ARG, "rope_append: null pointer");
     NF4_REQUIRE(Dh % 2 == 0 && Dh <= 2048 && Hq > 0 && Hkv > 0, NF4_ERR_ARG, "rope_append: bad head geometry");
+    NF4_REQUIRE(S_max > 0 && S_max <= 0x7fffffff, NF4_ERR_ARG, "rope_append: S_max=%lld", (long long)S_max);
     if (B == 0) return NF4_OK;
     dim3 grid((unsigned)(Hq + 2 * Hkv), (unsigned)B);
     rope_append_kernel<<<grid, Dh / 2, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -563,7 +590,8 @@ static int attn_configure() {
     static bool configured[64] = {false};
     int dev = 0;
     NF4_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 64 || configured[dev]) return NF4_OK;
+    NF4_REQUIRE(dev < 64, NF4_ERR_LIMIT, "attention: device ordinal %d (at most 64 devices per process)", dev);
+    if (configured[dev]) return NF4_OK;
 #define NF4_AT_OPT_IN(K) NF4_CUDA_TRY(cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES))
     NF4_AT_OPT_IN(attn_decode_kernel<1>); NF4_AT_OPT_IN(attn_decode_kernel<2>);
     NF4_AT_OPT_IN(attn_decode_kernel<4>); NF4_AT_OPT_IN(attn_decode_kernel<8>);
@@ -580,6 +608,7 @@ static int attn_decode_launch(const void* q, const void* k_cache, const void* v_
     NF4_REQUIRE(q && k_cache && v_cache && positions && out && workspace, NF4_ERR_ARG, "attn_decode: null pointer");
     NF4_REQUIRE(Dh == 128, NF4_ERR_ARG, "attn_decode: head_dim %d (only 128)", Dh);
     NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 32, NF4_ERR_ARG, "attn_decode: bad geometry (1 <= nsplit <= 32)");
+    NF4_REQUIRE(S_max > 0 && S_max <= 0x7fffffff, NF4_ERR_ARG, "attn_decode: S_max=%lld", (long long)S_max);
     if (B == 0) return NF4_OK;
     const int G = Hq / Hkv;
     if (int rc = attn_configure()) return rc;
@@ -658,6 +687,7 @@ extern "C" int nf4_b200_attn_decode_fused(const void* qkv, const int* positions,
     NF4_REQUIRE(qkv && positions && k_cache && v_cache && out && workspace && counters, NF4_ERR_ARG, "attn_decode_fused: null pointer");
     NF4_REQUIRE(Dh == 128, NF4_ERR_ARG, "attn_decode_fused: head_dim %d (only 128)", Dh);
     NF4_REQUIRE(Hkv > 0 && Hq % Hkv == 0 && nsplit >= 1 && nsplit <= 32, NF4_ERR_ARG, "attn_decode_fused: bad geometry (1 <= nsplit <= 32)");
+    NF4_REQUIRE(S_max > 0 && S_max <= 0x7fffffff, NF4_ERR_ARG, "attn_decode_fused: S_max=%lld", (long long)S_max);
     if (B == 0) return NF4_OK;
     const int G = Hq / Hkv;
     NF4_REQUIRE(G == 1 || G == 2 || G == 4 || G == 8, NF4_ERR_ARG, "attn_decode_fused: %d query heads per KV head", G);

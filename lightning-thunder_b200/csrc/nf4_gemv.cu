@@ -455,8 +455,8 @@ extern "C" int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const u
     NF4_REQUIRE(K >= 64 && K % 64 == 0 && N >= 1, NF4_ERR_ARG, "gemv_decode: bad extents N=%lld K=%lld", (long long)N, (long long)K);
     NF4_REQUIRE(prologue >= 0 && prologue <= 2, NF4_ERR_ARG, "gemv_decode: prologue %d", prologue);
     NF4_REQUIRE(prologue != 1 || norm_w, NF4_ERR_ARG, "gemv_decode: the rmsnorm prologue needs norm_w");
-    NF4_REQUIRE(epilogue == 0 || (epilogue == 1 && !residual && N % 2 == 0), NF4_ERR_ARG,
-                "gemv_decode: the SwiGLU epilogue takes an even N and no residual");
+    NF4_REQUIRE(epilogue == 0 || (epilogue == 1 && !residual && N % 2 == 0) || (epilogue == 2 && !residual && N % 16 == 0),
+                NF4_ERR_ARG, "gemv_decode: the SwiGLU epilogues take no residual and an even N (pairs) or N %% 16 == 0 (halves)");
     NF4_REQUIRE(gemv_supported(M, K, N, 64, NF4_BF16, x, packed, absmax), NF4_ERR_ALIGN,
                 "gemv_decode: x must be 16-byte aligned, packed 8-byte aligned");
     if (int rc = check_device()) return rc;

@@ -60,7 +60,8 @@ struct alignas(64) StagedParams {
     int prologue;    // 0: none; 1: x <- rmsnorm(x) * norm_w; 2: x <- silu(x[:, :K]) * x[:, K:2K]  (x is [M][2K])
     const void* norm_w;   // [K], prologue 1
     float eps;
-    int epilogue;    // 0: y[m][n]; 1: rows come in (gate, up) pairs and y[m][n/2] = silu(gate) * up
+    int epilogue;    // 0: y[m][n]; 1: rows come in (gate, up) pairs and y[m][n/2] = silu(gate) * up;
+                     // 2: rows [0, N/2) are gate, [N/2, N) up: a tile is 8 gate rows + the 8 matching up rows
     // offsets from the start of dynamic shared memory
     int off_bars, off_part, off_x;
     int h_base, h_rem;   // halves of 8 rows per CTA: h_base, plus one for the first h_rem CTAs
@@ -242,14 +243,18 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
 
     // rows are dealt out in halves of 8: a CTA owns [8*h0, 8*h1); full 16-row tiles first, then at
     // most one half tile
+    // (epilogue 2: the halves count gate rows; every half is a full tile with its 8 up rows)
     const int bid = (int)blockIdx.x;
+    const bool split_gu = p.epilogue == 2;
+    const int n_own = split_gu ? (p.N >> 1) : p.N;      // rows that are dealt out
+    const int tile_rows = split_gu ? 8 : 16;            // ... and how many of them one tile covers
     const int h0 = bid * p.h_base + min(bid, p.h_rem);
     const int h1 = h0 + p.h_base + (bid < p.h_rem ? 1 : 0);
     const int r0 = h0 * 8;
-    const int r1 = min(h1 * 8, p.N);
+    const int r1 = min(h1 * 8, n_own);
     const int nhalves = h1 - h0;
-    const int nfull = nhalves >> 1;
-    const int ntiles = nfull + (nhalves & 1);
+    const int nfull = split_gu ? nhalves : (nhalves >> 1);
+    const int ntiles = split_gu ? nhalves : nfull + (nhalves & 1);
 
     if (s0 > 2048u) {   // the host-side map assumes the dynamic region starts within 2 KB of the window
         if (tid == 0 && atomicCAS(&g_gemv_error[0], 0u, 4u) == 0u) g_gemv_error[1] = blockIdx.x;
@@ -288,12 +293,20 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                 for (int j = 0; j < nt_here; ++j) {
                     if (stage >= p.NS) mbar_wait(empty0 + slot * 8, parity ^ 1u, abort_flag, 2, stage);
                     if (lane == 0) {
-                        const int row0 = r0 + (tile0 + j) * 16;
+                        const int row0 = r0 + (tile0 + j) * tile_rows;
                         const uint32_t fullb = full0 + slot * 8;
                         const uint32_t sbase = ring_u32 + (uint32_t)slot * (uint32_t)p.stage_bytes;
                         mbar_expect_tx(fullb, (uint32_t)(half ? 8 : 16) * (uint32_t)(p.RS + p.AS));
-                        tma_load_2d(sbase, half ? &p.wmap8 : &p.wmap16, seg * p.SB * 4, row0, fullb);
-                        tma_load_2d(sbase + 16 * p.RS, half ? &p.amap8 : &p.amap16, seg * p.SB, row0, fullb);
+                        if (split_gu) {
+                            // rows 0..7 of the tile: gate rows row0.., rows 8..15: the up rows of the same outputs
+                            tma_load_2d(sbase, &p.wmap8, seg * p.SB * 4, row0, fullb);
+                            tma_load_2d(sbase + 8 * p.RS, &p.wmap8, seg * p.SB * 4, n_own + row0, fullb);
+                            tma_load_2d(sbase + 16 * p.RS, &p.amap8, seg * p.SB, row0, fullb);
+                            tma_load_2d(sbase + 16 * p.RS + 8 * p.AS, &p.amap8, seg * p.SB, n_own + row0, fullb);
+                        } else {
+                            tma_load_2d(sbase, half ? &p.wmap8 : &p.wmap16, seg * p.SB * 4, row0, fullb);
+                            tma_load_2d(sbase + 16 * p.RS, half ? &p.amap8 : &p.amap16, seg * p.SB, row0, fullb);
+                        }
                     }
                     __syncwarp();
                     ++stage;
@@ -528,6 +541,31 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
             return;
         }
+        if (p.epilogue == 2) {
+            // SwiGLU over split halves: rows 0..7 of a tile are gate_i, rows 8..15 the up_i of the same outputs
+            const int pairs = nt_here * Mc * 8;
+            for (int o = tid; o < pairs; o += CW * 32) {
+                const int pr = o & 7;
+                const int jm = o >> 3;
+                const int j = jm / Mc;
+                const int m = jm - j * Mc;
+                const int grow = r0 + (tile0 + j) * 8 + pr;
+                if (grow < r1) {
+                    float sg = 0.0f, su = 0.0f;
+                    const int idx = jm * 16 + pr;
+#pragma unroll
+                    for (int w = 0; w < CW; ++w) {
+                        sg += part[w * (TG * Mc * 16) + idx];
+                        su += part[w * (TG * Mc * 16) + idx + 8];
+                    }
+                    const float gt = Elem<T>::to_f32(Elem<T>::from_f32(sg));
+                    const float up = Elem<T>::to_f32(Elem<T>::from_f32(su));
+                    static_cast<T*>(p.y)[(int64_t)m * n_own + grow] = Elem<T>::from_f32(gt / (1.0f + __expf(-gt)) * up);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+            return;
+        }
         const int outputs = nt_here * Mc * 16;
         for (int o = tid; o < outputs; o += CW * 32) {
             const int row = o & 15;
@@ -709,10 +747,15 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     }
     const int NT = M <= 8 ? 1 : 2;
     const int sms = sm_count();
-    const int H = (N + 7) / 8;
+    if (opt.epilogue == 2 && (N % 16 != 0)) return -2;
+    const int H = opt.epilogue == 2 ? N / 16 : (N + 7) / 8;      // halves of 8 rows (epilogue 2: of 8 gate rows)
     int grid = sms;
-    if (grid > (H + 1) / 2) grid = (H + 1) / 2;
-    const int tiles = ((H + grid - 1) / grid + 1) / 2;
+    if (opt.epilogue == 2) {
+        if (grid > H) grid = H;
+    } else if (grid > (H + 1) / 2) {
+        grid = (H + 1) / 2;
+    }
+    const int tiles = opt.epilogue == 2 ? (H + grid - 1) / grid : ((H + grid - 1) / grid + 1) / 2;
     // 16 compute warps; 8 for two column tiles whose activations stay in global memory (more than fit
     // below the table): every group of tiles re-reads the activations from L2, so the groups are made
     // 4 tiles tall, which needs the registers of the 8-warp shape
@@ -806,7 +849,10 @@ template int gemv_staged_try<__half>(const void*, int, int, const uint8_t*, cons
 
 using namespace nf4;
 
-namespace nf4 { int gemm_read_error(unsigned int* out4); }
+namespace nf4 {
+int gemm_read_error(unsigned int* out4);
+int attn_read_error(unsigned int* out4);
+}
 
 extern "C" int nf4_b200_gemv_decode_fits(int64_t M, int64_t N, int64_t K, int prologue) {
     if (M < 1 || M > 16 || N < 1 || K < 64 || K % 64 != 0 || prologue < 0 || prologue > 2) return 0;
@@ -825,6 +871,11 @@ extern "C" int nf4_b200_device_error(unsigned int* host_out4) {
     if (host_out4[0] == 0) {   // no GEMV error: report the GEMM kernel's word
         unsigned int g[4] = {0, 0, 0, 0};
         if (int rc = gemm_read_error(g)) return rc;
+        for (int i = 0; i < 4; ++i) host_out4[i] = g[i];
+    }
+    if (host_out4[0] == 0) {   // nor a GEMM error: the attention kernels' word
+        unsigned int g[4] = {0, 0, 0, 0};
+        if (int rc = attn_read_error(g)) return rc;
         for (int i = 0; i < 4; ++i) host_out4[i] = g[i];
     }
     return NF4_OK;

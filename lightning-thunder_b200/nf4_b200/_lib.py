@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libnf4_b200.so")
 
 NF4_F32, NF4_F16, NF4_BF16 = 0, 1, 2
-HAS_SWIGLU_HALVES = False   # epilogue 2 of nf4_b200_gemv_decode
+HAS_SWIGLU_HALVES = True   # epilogue 2 of nf4_b200_gemv_decode
 
 _c_i64 = ctypes.c_int64
 _c_int = ctypes.c_int

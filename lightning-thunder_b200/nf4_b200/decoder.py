@@ -139,6 +139,7 @@ class NF4Decoder:
                 self.cand = torch.empty((B, 2), device=dev, dtype=torch.float32)
                 self.cand_all = torch.empty((tp_size, B, 2), device=dev, dtype=torch.float32)
         self.graph = None
+        self.next_pos = 0           # host mirror of the highest position the next step writes (see _guard)
         self.launches_per_step = 0
         self.gemv_events = None     # set to a list to collect (start, stop, algorithmic bytes) per GEMV launch
 
@@ -249,8 +250,24 @@ class NF4Decoder:
             b.record()
             self.gemv_events.append((a, b, w.nbytes() + 2 * M * (w.K + w.N)))
 
+    def _guard(self) -> None:
+        """The kernels index the KV cache at `positions`; refuse on the host to step past the cache."""
+        if self.next_pos >= self.S:
+            raise RuntimeError(f"NF4Decoder: the KV cache holds {self.S} positions and all are used; "
+                               "reset() or build the decoder with a larger max_seq")
+        self.next_pos += 1
+
+    def set_positions(self, pos: int) -> None:
+        """All sequences continue at cache row `pos` (rows below it keep their contents)."""
+        if not 0 <= pos < self.S:
+            raise ValueError(f"position {pos} outside the cache [0, {self.S})")
+        self.positions.fill_(pos)
+        self.next_pos = pos
+
     def step(self) -> None:
         """One decode step on the current stream: ids_in, positions -> ids_out; positions += 1."""
+        if not torch.cuda.is_current_stream_capturing():
+            self._guard()
         if self.fused:
             return self._step_fused()
         return self._step_unfused()
@@ -366,7 +383,9 @@ class NF4Decoder:
         also copies ids_out to ids_in inside the graph (a device-resident greedy loop); otherwise the
         host provides ids_in every step.  Returns the graph (several may be kept and swapped)."""
         # Warm-up outside capture: first calls create tensor maps, set kernel attributes, init NCCL.
-        pos0 = self.positions.clone()
+        pos0, next0 = self.positions.clone(), self.next_pos
+        if self.next_pos + 2 > self.S:
+            raise RuntimeError("NF4Decoder.capture: needs two free cache rows for its warm-up steps")
         s = torch.cuda.Stream(device=self.dev)
         s.wait_stream(torch.cuda.current_stream(self.dev))
         with torch.cuda.stream(s):
@@ -383,16 +402,19 @@ class NF4Decoder:
             if feed_back:
                 self.ids_in.copy_(self.ids_out)
         self.positions.copy_(pos0)
+        self.next_pos = next0
         return self.graph
 
     def run_step(self) -> None:
         if self.graph is not None:
+            self._guard()
             self.graph.replay()
         else:
             self.step()
 
     def reset(self) -> None:
         self.positions.zero_()
+        self.next_pos = 0
 
     def generate(self, prompt: torch.Tensor, n_new: int) -> torch.Tensor:
         """prompt [B, T] int64 (host or device).  Feeds the prompt one token per step (filling the KV

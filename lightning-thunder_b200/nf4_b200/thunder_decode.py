@@ -1,0 +1,78 @@
+"""The NF4 decode path through Thunder's own API: `compile_decoder(model)` is
+`thunder.jit(model, transforms=[...], executors=[...])` with the transform stack a serving loop wants,
+and `generate` is the prefill + token-by-token loop of the reference's inference benchmark
+(thunder/benchmarks/benchmark_inference.py:440-529: the whole prompt in one call, then one call per
+token with the sampled id fed back).
+
+Transform stack, in order:
+  NF4LinearQuant4bit      every nn.Linear -> NF4 weights + the `nf4_b200_matmul` symbol   (the drop-in for
+                          thunder.transforms.quantization.BitsAndBytesLinearQuant4bit)
+  NF4DecodeFusion         single-token traces: attention / MLP blocks -> fused kernels     (nf4_b200.fusion)
+  PrunePrologueChecks     drops the per-call re-validation of module members               (thunder/transforms/
+                          prune_prologue_checks.py, what thunder/recipes/base.py:103-112 installs)
+  CUDAGraphTransform      the computation replays as one CUDA graph                        (thunder/transforms/
+                          cudagraph.py:229-387, what the reduce-overhead plugin installs)
+"""
+
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from .fusion import NF4DecodeFusion
+from .thunder_executor import NF4LinearQuant4bit, get_nf4_executor, thunder
+
+
+class GreedyStep(nn.Module):
+    """model(tokens, input_pos) followed by argmax over the vocabulary: returns the next token ids
+    [B, 1] (int64), so a decode loop never brings logits to the host."""
+
+    def __init__(self, model: nn.Module):
+        super().__init__()
+        self.model = model
+
+    def forward(self, tokens: torch.Tensor, input_pos: torch.Tensor) -> torch.Tensor:
+        logits = self.model(tokens, input_pos)
+        return torch.argmax(logits[:, -1, :], dim=-1, keepdim=True)
+
+
+def compile_decoder(model: nn.Module, *, fuse: bool = True, cuda_graph: bool = True, prune_checks: bool = True,
+                    rope_theta: float | None = None, extra_transforms=(), **jit_kwargs):
+    """thunder.jit of `model` on the NF4 executor.  Returns the ThunderModule; `.nf4_fusion` is the
+    fusion pass (its `fused` / `declined` records say what was rewritten)."""
+    from thunder.transforms.cudagraph import CUDAGraphTransform
+    from thunder.transforms.prune_prologue_checks import PrunePrologueChecks
+
+    transforms = [NF4LinearQuant4bit()]
+    fusion = None
+    if fuse:
+        if rope_theta is None:
+            inner = getattr(model, "model", model)
+            rope_theta = getattr(getattr(inner, "args", None), "rope_theta", None)
+        fusion = NF4DecodeFusion(rope_theta=rope_theta)
+        transforms.append(fusion)
+    transforms += list(extra_transforms)
+    if prune_checks:
+        transforms.append(PrunePrologueChecks())
+    if cuda_graph:
+        transforms.append(CUDAGraphTransform())
+    jm = thunder.jit(model, transforms=transforms, executors=(get_nf4_executor(),), **jit_kwargs)
+    jm.nf4_fusion = fusion
+    return jm
+
+
+@torch.no_grad()
+def generate(jstep, prompt: torch.Tensor, n_new: int) -> torch.Tensor:
+    """Greedy decoding with a jitted GreedyStep: one call for the prompt [B, T] (prefill), then one call
+    per new token with the previous ids fed back on the device.  Returns [B, n_new] int64 (device)."""
+    B, T = prompt.shape
+    dev = prompt.device
+    out = torch.empty((B, n_new), dtype=torch.int64, device=dev)
+    tok = jstep(prompt, torch.arange(T, device=dev))
+    out[:, :1] = tok
+    pos = torch.tensor([T], device=dev)
+    for t in range(1, n_new):
+        tok = jstep(tok.clone(), pos)
+        out[:, t:t + 1] = tok
+        pos = pos + 1
+    return out

@@ -318,3 +318,39 @@ def test_next_weight_hint_changes_nothing(nf4_code_np):
     assert lib.nf4_b200_gemv_decode_next_weight(None, None, 0, 0) == 0
     torch.cuda.synchronize()
     assert _lib.device_error()[0] == 0
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 1024, 4096), (4, 14336, 4096), (8, 520, 2048), (16, 1024, 1024), (3, 8, 256)])
+def test_gemv_decode_swiglu_over_halves(M, F, K):
+    """Epilogue 2 (weight = [gate rows; up rows]) gives the bits of epilogue 1 on the same rows interleaved,
+    and both equal silu(gate) * up computed from the plain GEMV's bf16 outputs."""
+    import ctypes
+
+    import nf4_b200
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    g = torch.Generator(device="cuda").manual_seed(F + K + M)
+    wg = (torch.randn((F, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    wu = (torch.randn((F, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
+    ph, qh = nf4_b200.quantize_4bit(torch.cat([wg, wu], 0))
+    pi, qi = nf4_b200.quantize_4bit(torch.stack([wg, wu], 1).reshape(2 * F, K))
+    yh = torch.empty((M, F), device="cuda", dtype=torch.bfloat16)
+    yi = torch.empty_like(yh)
+    for flags in (0, 1):
+        yh.fill_(float("nan"))
+        _lib.check(lib.nf4_b200_gemv_decode(x.data_ptr(), M, K, ph.data_ptr(), qh.absmax.data_ptr(), qh.code.data_ptr(), 2 * F,
+                                            None, yh.data_ptr(), 0, None, 0.0, 2, flags, st), "gemv_decode halves")
+        _lib.check(lib.nf4_b200_gemv_decode(x.data_ptr(), M, K, pi.data_ptr(), qi.absmax.data_ptr(), qi.code.data_ptr(), 2 * F,
+                                            None, yi.data_ptr(), 0, None, 0.0, 1, flags, st), "gemv_decode pairs")
+        torch.cuda.synchronize()
+        assert torch.equal(yh, yi)
+    plain = nf4_b200.matmul_4bit(x, ph.t(), quant_state=qh).float()
+    want = plain[:, :F] / (1 + torch.exp(-plain[:, :F])) * plain[:, F:]
+    torch.testing.assert_close(yh.float(), want, rtol=1.6e-2, atol=1e-3)
+    assert _lib.device_error()[0] == 0
+    # N must be a multiple of 16 (whole 8-row boxes of gate and of up), and there is no residual term
+    assert lib.nf4_b200_gemv_decode(x.data_ptr(), M, K, ph.data_ptr(), qh.absmax.data_ptr(), qh.code.data_ptr(), 2 * F - 8,
+                                    None, yh.data_ptr(), 0, None, 0.0, 2, 0, st) == 1

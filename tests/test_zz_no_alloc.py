@@ -68,3 +68,18 @@ def test_static_scratch_refuses_oversized_shapes():
     d = ctypes.c_void_p(256)
     rc = lib.nf4_b200_attn_decode_static(d, d, d, d, d, 16, 64, 8, 128, 64, 9, None)   # one split too many
     assert rc == 6 and "built-in array" in _lib.last_error()
+
+
+def test_static_scratch_at_its_exact_maximum():
+    """The largest shape the built-in array holds (16 sequences x 64 query heads x 8 splits) runs and fills
+    every slot of it; one split more is refused (above)."""
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    B, Hq, Hkv, S_max, ns = 16, 64, 8, 200, 8
+    assert lib.nf4_b200_attn_decode_workspace_bytes(B, Hq, ns) == lib.nf4_b200_attn_decode_static_max_bytes()
+    lens = [200, 1, 7, 8, 9, 64, 65, 127, 128, 129, 150, 199, 16, 33, 100, 2]
+    q, k, v, pos = _inputs(3, B, Hq, Hkv, S_max, lens)
+    ref, out = _both(lib, _lib, q, k, v, pos, B, Hq, Hkv, S_max, ns)
+    assert torch.equal(out, ref)
+    assert _lib.device_error()[0] == 0
