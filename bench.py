@@ -315,47 +315,38 @@ def _log(msg):
         print(f"[bench rank {os.environ.get('RANK', '0')} {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
 
 
-def run_decode(args):
+WORKLOADS = {
+    # name: (config attribute, batch, prompt tokens, new tokens of the configuration)
+    "llama3-8b": ("LLAMA3_8B", 1, 512, 128),
+    "llama3-70b": ("LLAMA3_70B", 16, 1024, 256),
+    "tiny": (None, 1, 16, 16),
+}
+
+
+def metric_name(workload: str, world: int) -> str:
+    shape = {"llama3-8b": "Llama-3-8B shape", "llama3-70b": "Llama-3-70B shape", "tiny": "tiny test shape"}[workload]
+    tp = f", tensor parallel over {world} GPUs" if world > 1 else ""
+    return f"NF4 W4A16 decode tok/s ({shape}{tp}); dequant-GEMV HBM GB/s vs 8 TB/s"
+
+
+def engine_decode(cfg, batch, prompt_len, steps, warmup, dev, rank, world, group, *, feed_prompt=True, roofline=True,
+                  sampler=None):
+    """The decode engine (nf4_b200.decoder.NF4Decoder: this library's kernels called directly, one CUDA graph per
+    step).  Returns tok/s with the ids staying on the device, tok/s with host-fed ids, and the GEMV chain's
+    roofline figures."""
     import torch
 
     from nf4_b200 import _lib
-    from nf4_b200.decoder import LLAMA3_8B, LLAMA3_70B, NF4Decoder, tiny_config
+    from nf4_b200.decoder import NF4Decoder
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    torch.cuda.set_device(local)
-    dev = f"cuda:{local}"
-    group = None
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device(dev))
-        group = dist.group.WORLD
-
-    workload = args.workload or ("llama3-8b" if world == 1 else "llama3-70b")
-    if workload == "llama3-8b":
-        cfg, batch, prompt_len, new_tokens = LLAMA3_8B, 1, 512, 128
-    elif workload == "llama3-70b":
-        cfg, batch, prompt_len, new_tokens = LLAMA3_70B, 16, 1024, 256
-    else:
-        cfg, batch, prompt_len, new_tokens = tiny_config(), 1, 16, 16
-    if args.prompt is not None:
-        prompt_len = args.prompt
-    steps, warmup = args.steps, max(3, args.warmup)
-    max_seq = prompt_len + warmup + 2 * steps + 8
-
-    _log(f"building {cfg.name} tp{world}")
+    max_seq = prompt_len + warmup + 2 * steps + 16
     t_build = time.perf_counter()
     dec = NF4Decoder(cfg, batch=batch, max_seq=max_seq, device=dev, seed=1, tp_rank=rank, tp_size=world, group=group)
     torch.cuda.synchronize()
     t_build = time.perf_counter() - t_build
-
-    _log(f"built in {t_build:.1f}s; capturing")
+    _log(f"engine built in {t_build:.1f}s; capturing")
     g_host = dec.capture(feed_back=False)
     g_dev = dec.capture(feed_back=True)
-    _log("captured; filling the KV cache")
     launches = dec.launches_per_step
 
     def barrier():
@@ -363,26 +354,32 @@ def run_decode(args):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
-    # prompt -> KV cache, one token per step (the same decode path; no separate prefill kernel is timed)
     gen = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=gen)
     prompt_dev = prompt.to(dev)
     dec.reset()
     dec.graph = g_host
-    for t in range(prompt_len):
-        dec.ids_in.copy_(prompt_dev[:, t])
+    if feed_prompt:
+        # prompt -> KV cache, one token per step (the same decode path)
+        for t in range(prompt_len):
+            dec.ids_in.copy_(prompt_dev[:, t])
+            dec.run_step()
+    else:
+        # timing only: a cache of random rows up to the prompt length reads the same bytes as a real one
+        g = torch.Generator(device=dev).manual_seed(99)
+        for c in (dec.k_cache, dec.v_cache):
+            c[:, :, :, :prompt_len].copy_(torch.randn(c[:, :, :, :prompt_len].shape, generator=g, device=dev, dtype=torch.float32) * 0.5)
+        dec.set_positions(prompt_len)
+        dec.ids_in.copy_(prompt_dev[:, -1])
         dec.run_step()
     torch.cuda.synchronize()
 
-    _log("prompt done; timing")
-    # ---- device-resident greedy loop: `value`
     dec.graph = g_dev
     dec.ids_in.copy_(dec.ids_out)
     for _ in range(warmup):
         dec.run_step()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
+    if sampler is not None:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -395,9 +392,8 @@ def run_decode(args):
         t = torch.tensor([ms], device=dev)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t.item())
-    tok_s = steps * batch / (ms / 1e3)
 
-    # ---- end to end: every step the ids come from pinned host memory and the sampled ids go back
+    # host-fed ids: every step the ids come from pinned host memory and the sampled ids go back
     dec.graph = g_host
     ids_host = torch.empty((batch,), dtype=torch.int64).pin_memory()
     out_host = torch.empty((batch,), dtype=torch.int64).pin_memory()
@@ -416,8 +412,12 @@ def run_decode(args):
         t = torch.tensor([e2e_s], device=dev)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         e2e_s = float(t.item())
-    clocks = sampler.stop() if rank == 0 else None
-    e2e_tok_s = steps * batch / e2e_s
+    res = {"tok_s": steps * batch / (ms / 1e3), "ms_per_step": ms / steps, "e2e_tok_s": steps * batch / e2e_s,
+           "launches_per_step": launches, "build_s": t_build, "step_bytes": dec.weight_bytes()}
+    if not roofline:
+        del dec
+        torch.cuda.empty_cache()
+        return res
 
     # ---- roofline of the dominant kernel (the fused dequant-GEMV).  Algorithmic bytes of every GEMV launch
     # of a step come from one uncaptured step (a hook records them); the duration comes from a CUDA graph
@@ -450,10 +450,201 @@ def run_decode(args):
         c1.record(side)
         side.synchronize()
     chain_us = c0.elapsed_time(c1) * 1e3 / reps
-    gemv_us = [chain_us / len(ev)] * len(ev)
+    res.update({"gemv_bytes": gemv_bytes, "chain_us": chain_us, "device_error": list(_lib.device_error())})
+    del dec, chain
+    torch.cuda.empty_cache()
+    return res
+
+
+def thunder_decode(cfg, batch, prompt_len, steps, warmup, dev, sampler=None):
+    """The same workload through the reference's API: the Llama-shaped nn.Module (nf4_b200.llama) jitted by
+    thunder.jit with NF4LinearQuant4bit + NF4DecodeFusion + PrunePrologueChecks + CUDAGraphTransform on the NF4
+    executor (nf4_b200.thunder_decode.compile_decoder).  Timed as thunder/benchmarks/benchmark_inference.py:467-529
+    times decode: one module call per token, the sampled id fed back."""
+    import torch
+
+    from nf4_b200 import _lib
+    from nf4_b200.llama import LlamaArgs, LlamaDecoder
+    from nf4_b200.thunder_decode import GreedyStep, compile_decoder
+
+    max_seq = prompt_len + 2 * warmup + 2 * steps + 16
+    args = LlamaArgs(dim=cfg.d_model, n_layers=cfg.n_layers, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads,
+                     vocab_size=cfg.vocab, hidden_dim=cfg.ffn, norm_eps=cfg.norm_eps, rope_theta=cfg.rope_theta,
+                     max_seq_len=max_seq, max_batch=batch)
+    t0 = time.perf_counter()
+    with torch.device(dev):
+        model = LlamaDecoder(args).to(torch.bfloat16).eval().requires_grad_(False)
+    model.init_weights(seed=1)
+    model.reset_rope_tables()
+    jstep = compile_decoder(GreedyStep(model))
+    gen = torch.Generator().manual_seed(1234)
+    prompt_dev = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=gen).to(dev)
+    tok = torch.empty((batch, 1), dtype=torch.int64, device=dev)
+    pos = torch.zeros((1,), dtype=torch.int64, device=dev)
+    tok.copy_(prompt_dev[:, :1])
+    out = jstep(tok, pos)                       # first call: quantize, trace, fuse, capture
+    torch.cuda.synchronize()
+    t_first = time.perf_counter() - t0
+    _log(f"thunder: first call after {t_first:.1f}s")
+    # the rest of the prompt through the decode trace, token by token
+    for t in range(1, prompt_len):
+        tok.copy_(prompt_dev[:, t:t + 1])
+        pos.fill_(t)
+        out = jstep(tok, pos)
+    pos.fill_(prompt_len)
+    for _ in range(warmup):
+        out = jstep(out, pos)
+        pos.add_(1)
+    torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    e0.record()
+    for _ in range(steps):
+        out = jstep(out, pos)                   # ids stay on the device
+        pos.add_(1)
+    host_issue_s = time.perf_counter() - w0
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+
+    # end to end: ids and position come from pinned host memory every step, the sampled ids go back
+    ids_host = torch.empty((batch, 1), dtype=torch.int64).pin_memory()
+    pos_host = torch.empty((1,), dtype=torch.int64).pin_memory()
+    out_host = torch.empty((batch, 1), dtype=torch.int64).pin_memory()
+    ids_host.copy_(out.cpu())
+    p = int(pos.item())
+    for _ in range(warmup):
+        pos_host[0] = p
+        tok.copy_(ids_host, non_blocking=True)
+        pos.copy_(pos_host, non_blocking=True)
+        out = jstep(tok, pos)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        ids_host.copy_(out_host)
+        p += 1
+    torch.cuda.synchronize()
+    w0 = time.perf_counter()
+    for _ in range(steps):
+        pos_host[0] = p
+        tok.copy_(ids_host, non_blocking=True)
+        pos.copy_(pos_host, non_blocking=True)
+        out = jstep(tok, pos)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        ids_host.copy_(out_host)
+        p += 1
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - w0
+
+    # kernels per step: count the launches of one more call (outside the timed regions)
+    launches = None
+    try:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            jstep(tok, pos)
+            torch.cuda.synchronize()
+        launches = sum(1 for e in prof.events() if str(e.device_type).endswith("CUDA") and "Memcpy" not in e.name and "Memset" not in e.name)
+    except Exception as exc:      # noqa: BLE001 - the count is informative only
+        _log(f"kernel count unavailable: {exc}")
+    fusion = jstep.nf4_fusion
+    res = {"tok_s": steps * batch / (ms / 1e3), "ms_per_step": ms / steps, "e2e_tok_s": steps * batch / e2e_s,
+           "e2e_ms_per_step": 1e3 * e2e_s / steps, "host_issue_ms_per_step": 1e3 * host_issue_s / steps,
+           "launches_per_step": launches, "first_call_s": t_first, "fused_blocks": dict(fusion.fused),
+           "declined": list(fusion.declined), "h2d_bytes_per_step": 8 * batch + 8, "d2h_bytes_per_step": 8 * batch,
+           "device_error": list(_lib.device_error())}
+    del jstep, model
+    torch.cuda.empty_cache()
+    return res
+
+
+def tp_parity(world, rank, group, dev):
+    """Before timing a tensor-parallel run: the tiny configuration decoded at tp=world by all ranks and at tp=1 on
+    rank 0 from the same seeds; logits of the last step and the sampled ids of all steps are compared."""
+    import torch
+
+    from nf4_b200.decoder import NF4Decoder, tiny_config
+
+    cfg = tiny_config(n_layers=2, d_model=1024, n_heads=8, n_kv_heads=8, ffn=2048, vocab=4096)
+    B, steps = 2, 8
+    gen = torch.Generator().manual_seed(7)
+    first = torch.randint(0, cfg.vocab, (B,), generator=gen).to(dev)
+
+    def run(tp_rank, tp_size, grp):
+        dec = NF4Decoder(cfg, batch=B, max_seq=32, device=dev, seed=3, tp_rank=tp_rank, tp_size=tp_size, group=grp)
+        dec.ids_in.copy_(first)
+        ids = []
+        for _ in range(steps):
+            dec.step()
+            ids.append(dec.ids_out.clone())
+            dec.ids_in.copy_(dec.ids_out)
+        torch.cuda.synchronize()
+        return torch.stack(ids), dec.logits.float().clone()
+
+    ids_tp, logits_tp = run(rank, world, group)
+    gathered = [torch.empty_like(logits_tp) for _ in range(world)]
+    torch.distributed.all_gather(gathered, logits_tp, group=group)
+    if rank != 0:
+        return None
+    ids_1, logits_1 = run(0, 1, None)
+    full = torch.cat(gathered, dim=1)
+    return {"config": "2 layers, d 1024, 8 heads, ffn 2048, vocab 4096, batch 2, 8 greedy steps",
+            "max_abs_logit_diff": float((full - logits_1).abs().max()), "logit_scale": float(logits_1.abs().max()),
+            "tokens_equal": bool(torch.equal(ids_tp, ids_1)), "tolerance": "rtol 1.6e-2 / atol 1e-2 per linear; "
+            "partial sums are rounded to bf16 before the all-reduce"}
+
+
+def run_decode(args):
+    import torch
+
+    from nf4_b200 import decoder as D
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    workload = args.workload or ("llama3-8b" if world == 1 else "llama3-70b")
+    attr, batch, prompt_len, new_tokens = WORKLOADS[workload]
+    cfg = getattr(D, attr) if attr else D.tiny_config()
+    if args.prompt is not None:
+        prompt_len = args.prompt
+    steps, warmup = args.steps, max(3, args.warmup)
     peaks, src = measured_peaks()
-    achieved = sum(gemv_bytes) / chain_us / 1e3           # GB/s over all GEMV launches of a step
-    dev_err = _lib.device_error()
+
+    # Rank 0 does its host-only and single-GPU work BEFORE the process group exists: the other ranks wait in the
+    # rendezvous (a socket, no GPU work) instead of spinning a GPU in a collective.
+    cpu = anchor = None
+    if rank == 0:
+        _log("CPU baseline")
+        cpu = cpu_decode_sample(workload if workload != "tiny" else "llama3-8b", batch, 3)
+        if world > 1 and not args.no_anchor:
+            _log("tp1 anchor of the same workload")
+            anchor = engine_decode(cfg, batch, prompt_len, steps, warmup, dev, 0, 1, None, feed_prompt=False, roofline=False)
+    group = None
+    parity = None
+    if world > 1:
+        import datetime
+
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(minutes=30))
+        group = dist.group.WORLD
+        parity = tp_parity(world, rank, group, dev)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    th = None
+    if world == 1 and not args.no_thunder:
+        try:
+            th = thunder_decode(cfg, batch, prompt_len, steps, warmup, dev, sampler=sampler)
+        except ImportError as exc:
+            th = {"unavailable": f"thunder is not importable here: {exc}"}
+    eng = engine_decode(cfg, batch, prompt_len, steps, warmup, dev, rank, world, group, feed_prompt=(world == 1),
+                        sampler=sampler if (th is None or "unavailable" in th) else None)
+    clocks = sampler.stop() if sampler is not None else None
 
     def finish():
         # Tearing down NCCL communicators that captured graphs still reference can block at exit:
@@ -469,30 +660,52 @@ def run_decode(args):
         finish()
         return
 
-    cpu_tok_s, t_layer, cores, _ = cpu_decode_sample(workload if workload != "tiny" else "llama3-8b", batch, 3)
-    step_bytes = dec.weight_bytes()
+    cpu_tok_s, t_layer, cores, _ = cpu
+    gemv_bytes, chain_us = eng["gemv_bytes"], eng["chain_us"]
+    achieved = sum(gemv_bytes) / chain_us / 1e3           # GB/s over all GEMV launches of a step
+    use_thunder = th is not None and "unavailable" not in th
+    head = th if use_thunder else eng
     line = {
-        "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak" if world == 1 else "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(cfg.name, batch, prompt_len, world, step_bytes),
+        "metric": metric_name(workload, world), "value": head["tok_s"], "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(cfg.name, batch, prompt_len, world, eng["step_bytes"]),
         "clocks": clocks,
-        "e2e": {"value": e2e_tok_s, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 8 * batch},
-        "gpu_launches": launches * steps,
+        "path": ("thunder.jit(model, transforms=[NF4LinearQuant4bit, NF4DecodeFusion, PrunePrologueChecks, CUDAGraphTransform], "
+                 "executors=[quant_nf4_b200]) called once per token, ids fed back on the device") if use_thunder else
+                "decode engine (NF4Decoder: the C ABI called directly, one CUDA graph per step), ids fed back on the device",
+        "e2e": {"value": head["e2e_tok_s"], "unit": UNIT,
+                "h2d_bytes_per_step": th["h2d_bytes_per_step"] if use_thunder else 8 * batch,
+                "d2h_bytes_per_step": 8 * batch,
+                "path": "the jitted module called with token ids and position from pinned host memory; sampled ids read back each step"
+                        if use_thunder else "NF4Decoder.run_step() with ids from pinned host memory; sampled ids read back each step"},
+        "gpu_launches": (head["launches_per_step"] or eng["launches_per_step"]) * steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "peak_source": src,
                      "traffic": NCU_TRAFFIC_RATIO * sum(gemv_bytes) / len(gemv_bytes),
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 32064x4096, M=1 "
                                        "(74.88 MB for 73.95 MB algorithmic), scaled by algorithmic bytes",
-                     "kernel": "gemv_staged_kernel (fused NF4 dequant-GEMV)", "launches_per_step": len(ev),
-                     "avg_launch_us": sum(gemv_us) / len(gemv_us), "algorithmic_bytes_per_launch": sum(gemv_bytes) / len(gemv_bytes),
+                     "kernel": "gemv_staged_kernel (fused NF4 dequant-GEMV)", "launches_per_step": len(gemv_bytes),
+                     "avg_launch_us": chain_us / len(gemv_bytes), "algorithmic_bytes_per_launch": sum(gemv_bytes) / len(gemv_bytes),
                      "frac_of_8TBps": achieved / 8000.0,
-                     "whole_step_GBps": step_bytes / (ms / steps / 1e3) / 1e9},
+                     "whole_step_GBps": eng["step_bytes"] / (head["ms_per_step"] / 1e3) / 1e9},
         "cpu_baseline": {"value": cpu_tok_s, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"the 4 quantized linears of one decoder layer at M={batch} on the CPU oracle, median of 3 "
                                    f"passes ({t_layer * 1e3:.1f} ms each), scaled to all layers + output head"},
-        "build_s": t_build, "device_error": list(dev_err),
+        "engine": {"tok_s": eng["tok_s"], "ms_per_step": eng["ms_per_step"], "e2e_tok_s": eng["e2e_tok_s"],
+                   "launches_per_step": eng["launches_per_step"], "build_s": eng["build_s"]},
+        "device_error": eng["device_error"],
     }
+    if th is not None:
+        line["thunder"] = {k: v for k, v in th.items() if k != "device_error"}
+        if use_thunder:
+            line["thunder"]["vs_engine"] = th["tok_s"] / eng["tok_s"]
+    if anchor is not None:
+        line["tp1_same_workload_tok_s"] = anchor["tok_s"]
+        line["tp1_same_workload_ms_per_step"] = anchor["ms_per_step"]
+        line["speedup_vs_tp1_same_workload"] = eng["tok_s"] / anchor["tok_s"]
+    if parity is not None:
+        line["tp_parity"] = parity
     print(json.dumps(line))
     finish()
 
@@ -505,6 +718,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "llama3-8b", "llama3-70b", "tiny"])
     ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
+    ap.add_argument("--no-thunder", action="store_true", help="N = 1: time only the decode engine, not the jitted module")
+    ap.add_argument("--no-anchor", action="store_true", help="N > 1: skip the single-GPU run of the same workload")
     ap.add_argument("--kernel", default=None, choices=[None, "gemv", "gemm", "quantize", "dequantize", "attention"])
     ap.add_argument("--B", type=int, default=16, help="attention: sequences")
     ap.add_argument("--Hq", type=int, default=64, help="attention: query heads")
