@@ -110,8 +110,11 @@ int nf4_b200_gemm_decode(const void* x, int64_t M, int64_t K, const uint8_t* pac
  * values, one fp32 offset (device scalar).  The reference leaves this as a TODO
  * (thunder/transforms/quantization.py:84, 120); results are bit-exact with this library's CPU oracle.
  *   absmax' = fma(code256[absmax_u8[i]], scale2[i / 256], *offset)
- * nf4_b200_linear_dq expands absmax into `workspace` (nf4_b200_linear_dq_workspace_bytes(N, K) bytes)
- * and then runs nf4_b200_linear (blocksize 64).
+ * nf4_b200_linear_dq (blocksize 64): up to 16 activation rows in bf16 with K a multiple of 1024 run the fused
+ * dequant-GEMV with the 8-bit absmax expanded inside the kernel (the weight streams as 0.5 + 1/64 + 1/4096
+ * bytes per element and `workspace` is not touched); every other case expands absmax into `workspace`
+ * (nf4_b200_linear_dq_workspace_bytes(N, K) bytes) and then runs nf4_b200_linear on it -- for the tensor-core
+ * GEMM that pass is a few per cent of the multiplication.
  */
 int nf4_b200_dq_quantize(const float* absmax, int64_t nblocks, const float* code256, uint8_t* absmax_u8, float* scale2,
                          float* offset, void* stream);

@@ -124,6 +124,12 @@ extern "C" int nf4_b200_dq_dequantize(const uint8_t* absmax_u8, const float* sca
     return NF4_OK;
 }
 
+namespace nf4 {
+int gemv_dq_try(const void* x, int64_t M, int64_t K, const uint8_t* packed, const uint8_t* absmax_u8, const float* scale2,
+                const float* offset, const float* code256, const float* code16, int64_t N, const void* bias, void* y,
+                int dtype, cudaStream_t stream);
+}
+
 extern "C" int64_t nf4_b200_linear_dq_workspace_bytes(int64_t N, int64_t K) { return ((N * K + 63) / 64) * 4; }
 
 extern "C" int nf4_b200_linear_dq(const void* x, int64_t M, int64_t K, const uint8_t* packed, const uint8_t* absmax_u8,
@@ -132,6 +138,14 @@ extern "C" int nf4_b200_linear_dq(const void* x, int64_t M, int64_t K, const uin
                                   void* stream) {
     NF4_REQUIRE(M >= 0 && N >= 0 && K >= 0, NF4_ERR_ARG, "linear_dq: negative extent");
     if (M == 0 || N == 0) return NF4_OK;
+    NF4_REQUIRE(x && packed && absmax_u8 && scale2 && offset && code256 && code16 && y, NF4_ERR_ARG, "linear_dq: null pointer");
+    // up to 16 activation rows: the fused GEMV expands the 8-bit absmax inside its stages (no workspace traffic)
+    if (int rc = check_device()) return rc;
+    {
+        const int rc = gemv_dq_try(x, M, K, packed, absmax_u8, scale2, offset, code256, code16, N, bias, y, dtype,
+                                   static_cast<cudaStream_t>(stream));
+        if (rc >= 0) return rc;
+    }
     const int64_t nblocks = (N * K + 63) / 64;
     NF4_REQUIRE(workspace && workspace_bytes >= nblocks * 4, NF4_ERR_WORKSPACE,
                 "linear_dq: workspace of %lld bytes, need %lld (nf4_b200_linear_dq_workspace_bytes)",

@@ -468,6 +468,21 @@ extern "C" int nf4_b200_gemv_decode(const void* x, int64_t M, int64_t K, const u
                                      static_cast<cudaStream_t>(stream), opt);
 }
 
+// Fused GEMV on a double-quantized weight: the uint8 absmax indices are expanded inside the kernel's stages.
+// Returns -1 (nothing launched) when the shape or a pointer does not suit that kernel.
+namespace nf4 {
+int gemv_dq_try(const void* x, int64_t M, int64_t K, const uint8_t* packed, const uint8_t* absmax_u8, const float* scale2,
+                const float* offset, const float* code256, const float* code16, int64_t N, const void* bias, void* y,
+                int dtype, cudaStream_t stream) {
+    if (dtype != NF4_BF16 || M < 1 || M > 16 || K < 64 || K % 64 != 0 || N < 1) return -1;
+    if (!gemv_supported(M, K, N, 64, dtype, x, packed, code16)) return -1;
+    GemvOptions opt;
+    opt.dq_absmax_u8 = absmax_u8; opt.dq_scale2 = scale2; opt.dq_offset = offset; opt.dq_code256 = code256;
+    const int rc = gemv_staged_try<__nv_bfloat16>(x, (int)M, (int)K, packed, nullptr, code16, (int)N, bias, nullptr, y, stream, opt);
+    return rc < 0 ? -1 : rc;
+}
+}  // namespace nf4
+
 extern "C" int nf4_b200_gemv(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
                              const float* code16, int64_t N, const void* bias, void* y, int dtype, void* stream) {
     return nf4_b200_gemv_fused(x, M, K, packed, absmax, code16, N, bias, nullptr, y, dtype, stream);

@@ -91,6 +91,12 @@ struct GemvOptions {
     bool dry_run = false;         // plan only: report whether the shape (and prologue) fits
     // weight the NEXT launch on this stream will read: each CTA pulls the head of its share into L2
     // once its own loads have been issued (fills the HBM idle time around the kernel boundary)
+    // double-quantized absmax: uint8 indices [N*K/64], one fp32 scale per 256 of them, a device scalar offset
+    // and the 256-entry table; the `absmax` argument of the call is then unused
+    const uint8_t* dq_absmax_u8 = nullptr;
+    const float* dq_scale2 = nullptr;
+    const float* dq_offset = nullptr;
+    const float* dq_code256 = nullptr;
     const uint8_t* next_packed = nullptr;
     const float* next_absmax = nullptr;
     int next_N = 0, next_K = 0;

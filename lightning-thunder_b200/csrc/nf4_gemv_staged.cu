@@ -43,7 +43,12 @@ struct alignas(64) StagedParams {
     CUtensorMap amap16, amap8;   // absmax fp32 [N][K/64], boxes of 16 and 8 rows
     const void* x;
     const uint8_t* packed;
-    const float* absmax;
+    const float* absmax;     // fp32 [N*KB]; with double quantization: the uint8 indices (absmax_u8) instead
+    // double-quantized absmax (template flag DQ): absmax = fma(code256[u8], scale2[block / 256], *offset)
+    const uint8_t* absmax_u8;
+    const float* scale2;
+    const float* offset;
+    const float* code256;
     const float* code16;
     const void* bias;
     const void* residual;   // optional [M][N], added after the bias (may alias y)
@@ -64,6 +69,7 @@ struct alignas(64) StagedParams {
                      // 2: rows [0, N/2) are gate, [N/2, N) up: a tile is 8 gate rows + the 8 matching up rows
     // offsets from the start of dynamic shared memory
     int off_bars, off_part, off_x;
+    int off_c256;    // DQ: the 256-entry table of the second quantization (1 KB)
     int h_base, h_rem;   // halves of 8 rows per CTA: h_base, plus one for the first h_rem CTAs
     // L2 prefetch of the next launch's weights (null: none): same row split, applied to its N
     const uint8_t* pf_packed;
@@ -151,6 +157,11 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -160,19 +171,24 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // One stage of one warp: BPW 64-blocks of a 16-row tile.  Per block: 16 table lookups, 4 chained
 // MMAs per column tile (the chains of different blocks interleave), one scaling by the block's
 // absmax.  HALF: rows 8..15 of the tile do not exist (their fragment registers stay zero).
-template <typename T, int NT, int BPW, bool HALF>
+// DQ: the stage holds uint8 absmax indices; sc[bi][0/1] are the second-level scales of this lane's two rows
+// (fetched by the caller before it waited for the stage), c256 the shared-memory table, dq_off the offset.
+template <typename T, int NT, int BPW, bool HALF, bool DQ>
 __device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a_off)[BPW], const uint32_t (&am_off)[BPW],
                                               uint32_t rs8, uint32_t as8, uint32_t window_lane,
-                                              const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4]) {
+                                              const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4],
+                                              const float (&sc)[BPW][2], uint32_t c256, float dq_off) {
     uint2 wa[BPW], wb[BPW];
     float ama[BPW], amb[BPW];
 #pragma unroll
     for (int bi = 0; bi < BPW; ++bi) {
         wa[bi] = lds64(sbase + a_off[bi]);
-        ama[bi] = lds32f(sbase + am_off[bi]);
+        if (DQ) ama[bi] = fmaf(lds32f(c256 + 4u * lds8(sbase + am_off[bi])), sc[bi][0], dq_off);
+        else ama[bi] = lds32f(sbase + am_off[bi]);
         if (!HALF) {
             wb[bi] = lds64(sbase + a_off[bi] + rs8);
-            amb[bi] = lds32f(sbase + am_off[bi] + as8);
+            if (DQ) amb[bi] = fmaf(lds32f(c256 + 4u * lds8(sbase + am_off[bi] + as8)), sc[bi][1], dq_off);
+            else amb[bi] = lds32f(sbase + am_off[bi] + as8);
         }
     }
     float tmp[BPW][NT][4];
@@ -221,7 +237,7 @@ __device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a
         }
 }
 
-template <typename T, int NT, int TG, int CW>
+template <typename T, int NT, int TG, int CW, bool DQ>
 __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __grid_constant__ StagedParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int BPW = 32 / CW;          // 64-blocks of a stage per warp
@@ -347,6 +363,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                      x_row_bytes, xbar);
     }
     lut_build<T, CW>(lut_ptr, level, warp, lane);
+    float dq_off = 0.0f;
+    if (DQ) {
+        if (tid < 256) reinterpret_cast<float*>(smem + p.off_c256)[tid] = __ldg(p.code256 + tid);
+        dq_off = __ldg(p.offset);
+    }
+    const uint32_t c256 = s0 + (uint32_t)p.off_c256;
     // barriers armed (producer) and table complete (compute warps) for every compute warp after this
     asm volatile("bar.sync 2, %0;" ::"n"((CW + 1) * 32) : "memory");
     griddep_launch();
@@ -442,7 +464,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     for (int bi = 0; bi < BPW; ++bi) {
         const int b = min(warp + bi * CW, p.SB - 1);
         a_off[bi] = (uint32_t)(g * p.RS + b * 32 + q * 8);
-        am_off[bi] = (uint32_t)(16 * p.RS + g * p.AS + b * 4);
+        am_off[bi] = (uint32_t)(16 * p.RS + g * p.AS + b * (DQ ? 1 : 4));
     }
     const uint32_t rs8 = 8u * (uint32_t)p.RS, as8 = 8u * (uint32_t)p.AS;
     const uint32_t stage_bytes = (uint32_t)p.stage_bytes;
@@ -483,10 +505,27 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     };
 
     // one stage: wait for the box, compute, hand the slot back
-#define NF4_DO_STAGE(HALF_, XF_, ACC_)                                                                              \
+    // DQ: second-level scales of this lane's rows (g, g+8 of the tile starting at row0_) for its blocks of
+    // segment seg_: one scale per 256 consecutive first-level blocks of the flattened weight
+    auto load_scales = [&](float (&sc)[BPW][2], int row0_, int seg_) {
+        if (DQ) {
+#pragma unroll
+            for (int bi = 0; bi < BPW; ++bi) {
+                const int kb = seg_ * p.SB + min(warp + bi * CW, p.SB - 1);
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int row = min(split_gu ? row0_ + g + hh * n_own : row0_ + g + 8 * hh, p.N - 1);
+                    sc[bi][hh] = __ldg(p.scale2 + (((int64_t)row * p.KB + kb) >> 8));
+                }
+            }
+        }
+    };
+#define NF4_DO_STAGE(HALF_, XF_, ACC_, ROW0_, SEG_)                                                                 \
     do {                                                                                                           \
+        float sc_[BPW][2];                                                                                         \
+        load_scales(sc_, ROW0_, SEG_);                                                                             \
         mbar_wait(full0 + slot * 8, parity, abort_flag, 1, stage);                                                  \
-        stage_compute<T, NT, BPW, HALF_>(ring_u32 + slot * stage_bytes, a_off, am_off, rs8, as8, window_lane, XF_, ACC_); \
+        stage_compute<T, NT, BPW, HALF_, DQ>(ring_u32 + slot * stage_bytes, a_off, am_off, rs8, as8, window_lane, XF_, ACC_, sc_, c256, dq_off); \
         __syncwarp();                                                                                              \
         if (lane == 0) mbar_arrive(empty0 + slot * 8);                                                              \
         ++stage;                                                                                                   \
@@ -602,7 +641,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             uint32_t xf[BPW][NT][8];
             load_xf(xf, seg);
 #pragma unroll
-            for (int j = 0; j < TG; ++j) NF4_DO_STAGE(false, xf, acc[j]);
+            for (int j = 0; j < TG; ++j) NF4_DO_STAGE(false, xf, acc[j], r0 + (tile0 + j) * tile_rows, seg);
         }
         finish_group(tile0, TG);
     }
@@ -615,7 +654,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             load_xf(xf, seg);
 #pragma unroll
             for (int j = 0; j < TG; ++j)
-                if (j < nt_here) NF4_DO_STAGE(false, xf, acc[j]);
+                if (j < nt_here) NF4_DO_STAGE(false, xf, acc[j], r0 + (tile0 + j) * tile_rows, seg);
         }
         finish_group(tile0, nt_here);
         tile0 = nfull;
@@ -626,7 +665,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
         for (int seg = 0; seg < p.nseg; ++seg) {
             uint32_t xf[BPW][NT][8];
             load_xf(xf, seg);
-            NF4_DO_STAGE(true, xf, acc[0]);
+            NF4_DO_STAGE(true, xf, acc[0], r0 + tile0 * 16, seg);
         }
         finish_group(tile0, 1);
     }
@@ -637,13 +676,14 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
 
 static thread_local bool g_launch_pdl = false;   // set by the entry point for the duration of one call
 
-template <typename T, int NT, int TG, int CW>
-static int launch_staged(const StagedParams& p, int grid, cudaStream_t stream) {
+template <typename T, int NT, int TG, int CW, bool DQ>
+static int launch_staged_dq(const StagedParams& p, int grid, cudaStream_t stream) {
     static bool configured[64] = {false};
     int dev = 0;
     NF4_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
-        NF4_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<T, NT, TG, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM));
+    NF4_REQUIRE(dev < 64, NF4_ERR_LIMIT, "gemv: device ordinal %d (at most 64 devices per process)", dev);
+    if (!configured[dev]) {
+        NF4_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<T, NT, TG, CW, DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM));
         configured[dev] = true;
     }
     if (g_launch_pdl) {
@@ -657,12 +697,21 @@ static int launch_staged(const StagedParams& p, int grid, cudaStream_t stream) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_staged_kernel<T, NT, TG, CW>, p));
+        NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_staged_kernel<T, NT, TG, CW, DQ>, p));
     } else {
-        gemv_staged_kernel<T, NT, TG, CW><<<grid, (CW + 1) * 32, GEMV_SMEM, stream>>>(p);
+        gemv_staged_kernel<T, NT, TG, CW, DQ><<<grid, (CW + 1) * 32, GEMV_SMEM, stream>>>(p);
     }
     NF4_CUDA_TRY(cudaGetLastError());
     return NF4_OK;
+}
+
+// the double-quantized form exists for bf16 only (the type of every configuration that uses it)
+template <typename T, int NT, int TG, int CW>
+static int launch_staged(const StagedParams& p, int grid, cudaStream_t stream) {
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        if (p.absmax_u8) return launch_staged_dq<T, NT, TG, CW, true>(p, grid, stream);
+    }
+    return launch_staged_dq<T, NT, TG, CW, false>(p, grid, stream);
 }
 
 // ---- tensor maps ----------------------------------------------------------------------------
@@ -688,14 +737,14 @@ struct MapSet { CUtensorMap w16, w8, a16, a8; };
 
 // One set of maps per (weight pointer, absmax pointer, N, K, SB); a map encodes only address and
 // geometry, so it stays valid when the buffer's contents change.
-static int get_maps(const uint8_t* packed, const float* absmax, int N, int K, int SB, const MapSet** out) {
+static int get_maps(const uint8_t* packed, const void* absmax, bool dq, int N, int K, int SB, MapSet* out) {
     typedef std::tuple<const void*, const void*, int, int, int, int> Key;
     static std::map<Key, MapSet> cache;
     static std::mutex mu;
     int dev = 0;
     NF4_CUDA_TRY(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(mu);
-    const Key key(packed, absmax, N, K, SB, dev);
+    const Key key(packed, absmax, N, K, dq ? -SB : SB, dev);
     auto it = cache.find(key);
     if (it == cache.end()) {
         EncodeTiledFn enc = encode_fn();
@@ -713,17 +762,19 @@ static int get_maps(const uint8_t* packed, const float* absmax, int N, int K, in
                              wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             NF4_REQUIRE(r == CUDA_SUCCESS, NF4_ERR_CUDA, "gemv: cuTensorMapEncodeTiled(weights) failed with %d", (int)r);
+            // absmax: fp32 [N][KB] in boxes of SB + 4 values, or (double quantization) uint8 [N][KB] in boxes of SB + 16
             const cuuint64_t adim[2] = {(cuuint64_t)KB, (cuuint64_t)N};
-            const cuuint64_t astr[1] = {(cuuint64_t)KB * 4};
-            const cuuint32_t abox[2] = {(cuuint32_t)(SB + 4), rows};
-            r = enc(i == 0 ? &ms.a16 : &ms.a8, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(absmax), adim, astr, abox,
+            const cuuint64_t astr[1] = {(cuuint64_t)KB * (dq ? 1 : 4)};
+            const cuuint32_t abox[2] = {(cuuint32_t)(dq ? SB + 16 : SB + 4), rows};
+            r = enc(i == 0 ? &ms.a16 : &ms.a8, dq ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                    const_cast<void*>(absmax), adim, astr, abox,
                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             NF4_REQUIRE(r == CUDA_SUCCESS, NF4_ERR_CUDA, "gemv: cuTensorMapEncodeTiled(absmax) failed with %d", (int)r);
         }
         it = cache.emplace(key, ms).first;
     }
-    *out = &it->second;
+    *out = it->second;      // copied while the lock is held: another thread may clear the cache
     return NF4_OK;
 }
 
@@ -734,16 +785,24 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
                     const void* bias, const void* residual, void* y, cudaStream_t stream, const GemvOptions& opt) {
     const int KB = K / 64;
     if (KB % 4 != 0) return -1;
-    if (reinterpret_cast<uintptr_t>(packed) % 16 || reinterpret_cast<uintptr_t>(absmax) % 16 ||
+    const bool dq = opt.dq_absmax_u8 != nullptr;
+    const void* am_ptr = dq ? static_cast<const void*>(opt.dq_absmax_u8) : static_cast<const void*>(absmax);
+    if (reinterpret_cast<uintptr_t>(packed) % 16 || reinterpret_cast<uintptr_t>(am_ptr) % 16 ||
         reinterpret_cast<uintptr_t>(x) % 16)
         return -1;
     int SB = 0;
-    for (int c = 32; c >= 8; c -= 4)
-        if (KB % c == 0) { SB = c; break; }
+    if (dq) {
+        // uint8 absmax rows: the row pitch (KB bytes) and the box width (SB + 16 bytes) must be multiples of 16
+        if (!std::is_same<T, __nv_bfloat16>::value || KB % 16 != 0) return -1;
+        SB = KB % 32 == 0 ? 32 : 16;
+    } else {
+        for (int c = 32; c >= 8; c -= 4)
+            if (KB % c == 0) { SB = c; break; }
+    }
     if (SB == 0) return -1;
     if (const char* env = getenv("NF4_GEMV_SB")) {   // tuning override: blocks per stage
         const int v = atoi(env);
-        if (v >= 8 && v <= 32 && v % 4 == 0 && KB % v == 0) SB = v;
+        if (v >= 8 && v <= 32 && v % 4 == 0 && KB % v == 0 && !dq) SB = v;
     }
     const int NT = M <= 8 ? 1 : 2;
     const int sms = sm_count();
@@ -774,6 +833,7 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
 
     StagedParams p;
     p.x = x; p.packed = packed; p.absmax = absmax; p.code16 = code16; p.bias = bias; p.residual = residual; p.y = y;
+    p.absmax_u8 = opt.dq_absmax_u8; p.scale2 = opt.dq_scale2; p.offset = opt.dq_offset; p.code256 = opt.dq_code256;
     p.M = M; p.N = N; p.K = K; p.KB = KB; p.SB = SB; p.nseg = KB / SB;
     p.h_base = H / grid;
     p.h_rem = H % grid;
@@ -792,7 +852,7 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         }
     }
     p.RS = SB * 32 + 32;
-    p.AS = SB * 4 + 16;
+    p.AS = dq ? SB + 16 : SB * 4 + 16;
     p.stage_bytes = 16 * p.RS + 16 * p.AS;
     p.prologue = opt.prologue; p.norm_w = opt.norm_w; p.eps = opt.eps; p.epilogue = opt.epilogue;
     if (opt.epilogue == 1 && (N % 2 != 0)) return -2;
@@ -802,7 +862,8 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     // above it: the ring (every stage and both boxes inside it start on a 128-byte boundary).
     const int low_cap = LUT_WINDOW - 2048;           // leaves room for the window's start offset
     p.off_bars = 0;
-    p.off_part = 256;
+    p.off_c256 = 256;
+    p.off_part = dq ? 256 + 1024 : 256;
     const int part_bytes = CW * TG * M * 16 * 4;
     p.off_x = (p.off_part + part_bytes + 127) & ~127;
     if (p.off_x > low_cap) return -1;
@@ -818,9 +879,9 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     }
     p.NS = NS;
     if (opt.dry_run) return NF4_OK;
-    const MapSet* ms = nullptr;
-    if (int rc = get_maps(packed, absmax, N, K, SB, &ms)) return rc;
-    p.wmap16 = ms->w16; p.wmap8 = ms->w8; p.amap16 = ms->a16; p.amap8 = ms->a8;
+    MapSet ms;
+    if (int rc = get_maps(packed, am_ptr, dq, N, K, SB, &ms)) return rc;
+    p.wmap16 = ms.w16; p.wmap8 = ms.w8; p.amap16 = ms.a16; p.amap8 = ms.a8;
 
     g_launch_pdl = opt.pdl;
 #define NF4_SG(NT_, TG_)                                                        \

@@ -180,20 +180,21 @@ _WORKSPACES: dict = {}
 
 
 def _linear_workspace(lib, M: int, N: int, K: int, dtype_code: int, device, stream_ptr):
-    """Zero-initialised split-K scratch for (device, stream), grown on demand.  The kernels return it to
-    its initial state, so one buffer serves every call on that stream.  While a CUDA graph is being
+    """Zero-initialised split-K scratch for (device, stream), grown on demand (earlier buffers are kept, never
+    freed).  The kernels return it to its initial state, so one buffer serves every call on that stream.  While a CUDA graph is being
     captured no new buffer is created (it would belong to the graph's pool): the call then runs without
     a K split unless a large enough buffer already exists."""
     need = int(lib.nf4_b200_linear_workspace_bytes(M, N, K, dtype_code))
     if need == 0:
         return None, 0
     key = (torch.device(device).index, stream_ptr.value if hasattr(stream_ptr, "value") else int(stream_ptr or 0))
-    ws = _WORKSPACES.get(key)
-    if ws is None or ws.numel() < need:
+    held = _WORKSPACES.setdefault(key, [])
+    if not held or held[-1].numel() < need:
         if torch.cuda.is_current_stream_capturing():
             return None, 0
-        ws = torch.zeros((max(need, 1 << 22),), dtype=torch.uint8, device=device)
-        _WORKSPACES[key] = ws
+        # superseded buffers stay alive: a CUDA graph captured earlier has their address baked in
+        held.append(torch.zeros((max(need, 1 << 22),), dtype=torch.uint8, device=device))
+    ws = held[-1]
     return ws, ws.numel()
 
 
@@ -207,6 +208,11 @@ def linear_nf4(x: torch.Tensor, packed: torch.Tensor, bias, absmax: torch.Tensor
         raise ValueError(f"linear_nf4: unsupported dtype {x.dtype}")
     _require_cuda(x, "linear_nf4 input")
     _require_cuda(packed, "linear_nf4 weight")
+    for name, t in (("weight", packed), ("absmax", absmax), ("code", code)):
+        if not t.is_cuda or t.device != x.device:
+            raise RuntimeError(f"linear_nf4: {name} is on {t.device}, the activations on {x.device}")
+    if absmax.dtype != torch.float32 or code.dtype != torch.float32:
+        raise RuntimeError(f"linear_nf4: absmax and code must be fp32 (got {absmax.dtype}, {code.dtype})")
     x2 = x.reshape(-1, K)
     if not x2.is_contiguous():
         x2 = x2.contiguous()
@@ -238,32 +244,56 @@ def matmul_4bit(A: torch.Tensor, B: torch.Tensor, quant_state: QuantState, out=N
     return linear_nf4(A, B, bias, quant_state.absmax, quant_state.code, quant_state.blocksize, quant_state.shape, out=out)
 
 
+_DQ_WORKSPACES: dict = {}
+
+
+def _dq_workspace(device, need: int) -> torch.Tensor:
+    """Scratch for the expanded absmax of the tensor-core path, one buffer per device, grown on demand and
+    never freed (a captured CUDA graph may hold the address of an earlier, smaller one)."""
+    key = torch.device(device).index
+    held = _DQ_WORKSPACES.setdefault(key, [])
+    if not held or held[-1].numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("linear_nf4_dq: the absmax workspace would have to grow during CUDA graph capture; "
+                               "run the call once outside of the capture first")
+        held.append(torch.empty((max(need, 1 << 22),), dtype=torch.uint8, device=device))
+    return held[-1]
+
+
 def linear_nf4_dq(x: torch.Tensor, packed: torch.Tensor, bias, state: QuantState, out=None, workspace=None) -> torch.Tensor:
-    """linear_nf4 for a double-quantized state (C entry point nf4_b200_linear_dq): absmax is expanded
-    into `workspace` (fp32, one value per 64 weights) and the regular kernels run on it."""
+    """linear_nf4 for a double-quantized state (C entry point nf4_b200_linear_dq).  Up to 16 activation rows
+    (bf16, K a multiple of 1024) the fused GEMV expands the 8-bit absmax inside its stages; otherwise absmax
+    is expanded into `workspace` (fp32, one value per 64 weights) and the regular kernels run on it."""
     N, K = int(state.shape[0]), int(state.shape[1])
     if x.shape[-1] != K:
         raise RuntimeError(f"linear_nf4_dq: x.shape={tuple(x.shape)} does not match weight shape {(N, K)}")
     if state.blocksize != 64:
         raise NotImplementedError("linear_nf4_dq: blocksize 64 only")
     _require_cuda(x, "linear_nf4_dq input")
+    for name, t, dt in (("weight", packed, torch.uint8), ("absmax", state.absmax, torch.uint8),
+                        ("scale", state.state2.absmax, torch.float32), ("offset", state.offset, torch.float32),
+                        ("code256", state.state2.code, torch.float32), ("code", state.code, torch.float32)):
+        if not t.is_cuda or t.device != x.device or t.dtype != dt:
+            raise RuntimeError(f"linear_nf4_dq: {name} must be a {dt} tensor on {x.device} (got {t.dtype} on {t.device})")
     x2 = x.reshape(-1, K)
     if not x2.is_contiguous():
         x2 = x2.contiguous()
+    M = x2.shape[0]
     if bias is not None and bias.dtype != x.dtype:
         bias = bias.to(x.dtype)
     lib = _lib.load()
     with torch.cuda.device(x.device):
-        need = lib.nf4_b200_linear_dq_workspace_bytes(N, K)
-        if workspace is None:
-            workspace = torch.empty((need,), dtype=torch.uint8, device=x.device)
+        fused = M <= 16 and x.dtype == torch.bfloat16 and K % 1024 == 0
+        if workspace is None and not fused:
+            workspace = _dq_workspace(x.device, int(lib.nf4_b200_linear_dq_workspace_bytes(N, K)))
         if out is None:
             out = torch.empty((*x.shape[:-1], N), dtype=x.dtype, device=x.device)
         _lib.check(
-            lib.nf4_b200_linear_dq(x2.data_ptr(), x2.shape[0], K, packed.data_ptr(), state.absmax.data_ptr(),
+            lib.nf4_b200_linear_dq(x2.data_ptr(), M, K, packed.data_ptr(), state.absmax.data_ptr(),
                                    state.state2.absmax.data_ptr(), state.offset.data_ptr(), state.state2.code.data_ptr(),
                                    state.code.data_ptr(), N, bias.data_ptr() if bias is not None else None, out.data_ptr(),
-                                   _DTYPE_CODE[x.dtype], workspace.data_ptr(), workspace.numel(), _stream_ptr(x.device)),
+                                   _DTYPE_CODE[x.dtype], workspace.data_ptr() if workspace is not None else None,
+                                   workspace.numel() if workspace is not None else 0, _stream_ptr(x.device)),
             "nf4_b200_linear_dq",
         )
     return out

@@ -1,7 +1,7 @@
 """Bring-up of Thunder where its optional dependencies are missing.
 
 `bootstrap()` makes `import thunder` work: it looks for Thunder on sys.path, then in
-`baseline/_ref` (a `pip install --target` of the reference, see DESIGN), and puts small pure-Python
+`baseline/_ref` (a `pip install --target` of the reference), and puts small pure-Python
 stand-ins for `optree`, `looseversion`, `lightning_utilities` and `opt_einsum` on sys.path when
 the real packages are absent.  Real `optree` is a C extension and therefore opaque to Thunder's
 bytecode interpreter; the stand-in is Python, so its entry points are registered as opaque

@@ -51,7 +51,7 @@ def test_dq_edge_cases():
 
 @pytest.mark.parametrize("M", [1, 16, 64])
 def test_linear_on_double_quantized_weight(nf4_code_np, M):
-    """Config 2 of the benchmark set uses double-quantized weights: y against the oracle's linear on
+    """The second benchmark configuration uses double-quantized weights: y against the oracle's linear on
     the oracle's expanded absmax."""
     import nf4_b200
     from nf4_b200.codebook import dq_code256
@@ -70,3 +70,58 @@ def test_linear_on_double_quantized_weight(nf4_code_np, M):
     torch.testing.assert_close(y.float().cpu(), ref, rtol=1.6e-2, atol=1e-2)
     deq = nf4_b200.dequantize_4bit(packed, qs)
     assert np.array_equal(bf16_bits(deq).reshape(-1), oracle.dequantize(p_np, a2, nf4_code_np, N * K, 64, out="bf16"))
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("M", [1, 4, 16, 256])
+def test_sweep_shapes_with_double_quant(nf4_code_np, M, N, K):
+    """The weight shapes and activation-row counts of the linear sweep with double quantization ON: up to 16 rows
+    the 8-bit absmax is expanded inside the fused GEMV (no workspace), above that it is expanded once and the
+    tensor-core GEMM runs.  Output rows are sampled against the oracle's linear on the oracle's expanded absmax,
+    in the kernel's own rounding mode and in the dequantize-then-matmul mode."""
+    import nf4_b200
+    from nf4_b200 import _lib
+    from nf4_b200.codebook import dq_code256
+
+    code256 = np.array(dq_code256(), np.float32)
+    w = seeded_weight((N, K), N + K + 11)
+    x = seeded_act((M, K), M + 21)
+    packed, qs = nf4_b200.quantize_4bit(w.cuda(), compress_statistics=True)
+    y = nf4_b200.matmul_4bit(x.cuda(), packed.t(), quant_state=qs)
+    torch.cuda.synchronize()
+    assert _lib.device_error()[0] == 0
+    p_np, a_np = oracle.quantize(bf16_bits(w), nf4_code_np, 64)
+    u8, scale2, offset = oracle.dq_quantize(a_np, code256, 256)
+    assert np.array_equal(qs.absmax.cpu().numpy(), u8)
+    a2 = oracle.dq_dequantize(u8, scale2, offset, code256, 256)
+    rows = sorted(set([0, M - 1, M // 2] + ([17, 255] if M > 255 else [])))
+    xs = x[rows]
+    for mode in (oracle.linear_mode_for(M), oracle.REF_DEQUANT_MATMUL_MODE):
+        ref = bits_to_bf16(oracle.linear_bf16(bf16_bits(xs), p_np, a2, nf4_code_np, N, K, 64, mode=mode)).float()
+        torch.testing.assert_close(y[rows].float().cpu(), ref, rtol=1.6e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("M", [1, 16, 2048])
+def test_output_head_shape_with_double_quant(nf4_code_np, M):
+    """128256 x 4096 with double quantization on: sampled output columns (a slice of weight rows through the
+    oracle -- the whole product would take the CPU minutes)."""
+    import nf4_b200
+    from nf4_b200.codebook import dq_code256
+
+    code256 = np.array(dq_code256(), np.float32)
+    N, K = 128256, 4096
+    g = torch.Generator(device="cuda").manual_seed(4)
+    w = (torch.randn((N, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
+    packed, qs = nf4_b200.quantize_4bit(w, compress_statistics=True)
+    y = nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs)
+    torch.cuda.synchronize()
+    a2 = nf4_b200.functional.expand_absmax(qs).cpu().numpy()
+    p_all = packed.cpu().numpy().reshape(N, K // 2)
+    rows_x = sorted(set([0, M - 1, M // 3]))
+    for r0 in (0, 64000, N - 256):                      # 256-row slices: first, middle, ragged end of the grid
+        p_np = np.ascontiguousarray(p_all[r0:r0 + 256]).reshape(-1)
+        a_np = np.ascontiguousarray(a2.reshape(N, K // 64)[r0:r0 + 256]).reshape(-1)
+        for mode in (oracle.linear_mode_for(M), oracle.REF_DEQUANT_MATMUL_MODE):
+            ref = bits_to_bf16(oracle.linear_bf16(bf16_bits(x[rows_x].cpu()), p_np, a_np, nf4_code_np, 256, K, 64, mode=mode)).float()
+            torch.testing.assert_close(y[rows_x][:, r0:r0 + 256].float().cpu(), ref, rtol=1.6e-2, atol=1e-2)

@@ -99,7 +99,7 @@ def test_bf16_input_path_matches_f32_path(nf4_code_np):
 
 
 def test_config1_golden(nf4_code_np):
-    """Configuration 1 of the task: W [4096,4096] N(0,0.02) bf16, x [16,4096] N(0,1), blocksize 64."""
+    """The first benchmark configuration: W [4096,4096] N(0,0.02) bf16, x [16,4096] N(0,1), blocksize 64."""
     with open(os.path.join(GOLDEN, "config1.json")) as f:
         g = json.load(f)
     N, K = g["shape"]
