@@ -339,9 +339,10 @@ def engine_decode(cfg, batch, prompt_len, steps, warmup, dev, rank, world, group
     from nf4_b200 import _lib
     from nf4_b200.decoder import NF4Decoder
 
-    max_seq = prompt_len + warmup + 2 * steps + 16
+    max_seq = prompt_len + 2 * warmup + 3 * steps + 32
     t_build = time.perf_counter()
-    dec = NF4Decoder(cfg, batch=batch, max_seq=max_seq, device=dev, seed=1, tp_rank=rank, tp_size=world, group=group)
+    dec = NF4Decoder(cfg, batch=batch, max_seq=max_seq, device=dev, seed=1, tp_rank=rank, tp_size=world, group=group,
+                     tp_reduce=os.environ.get("NF4_TP_REDUCE", "oneshot"))
     torch.cuda.synchronize()
     t_build = time.perf_counter() - t_build
     _log(f"engine built in {t_build:.1f}s; capturing")
@@ -414,6 +415,27 @@ def engine_decode(cfg, batch, prompt_len, steps, warmup, dev, rank, world, group
         e2e_s = float(t.item())
     res = {"tok_s": steps * batch / (ms / 1e3), "ms_per_step": ms / steps, "e2e_tok_s": steps * batch / e2e_s,
            "launches_per_step": launches, "build_s": t_build, "step_bytes": dec.weight_bytes()}
+    if world > 1 and dec.oneshot is not None:
+        # the same engine with the library all-reduce (NCCL) in place of the one-shot exchange over peer memory
+        res["exchange"] = "one-shot all-reduce over peer memory (nf4_b200_tp_allreduce)"
+        saved, dec.oneshot = dec.oneshot, None
+        g_nccl = dec.capture(feed_back=True)
+        dec.graph = g_nccl
+        dec.ids_in.copy_(dec.ids_out)
+        for _ in range(warmup):
+            dec.run_step()
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            dec.run_step()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        res["nccl_exchange_tok_s"] = steps * batch / (float(t.item()) / 1e3)
+        res["nccl_exchange_ms_per_step"] = float(t.item()) / steps
+        dec.oneshot = saved
+        del g_nccl
     if not roofline:
         del dec
         torch.cuda.empty_cache()
@@ -706,6 +728,9 @@ def run_decode(args):
         line["speedup_vs_tp1_same_workload"] = eng["tok_s"] / anchor["tok_s"]
     if parity is not None:
         line["tp_parity"] = parity
+    if "nccl_exchange_tok_s" in eng:
+        line["exchange"] = {"kind": eng["exchange"], "tok_s": eng["tok_s"], "nccl_all_reduce_tok_s": eng["nccl_exchange_tok_s"],
+                            "nccl_all_reduce_ms_per_step": eng["nccl_exchange_ms_per_step"]}
     print(json.dumps(line))
     finish()
 

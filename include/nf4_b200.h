@@ -226,11 +226,37 @@ int nf4_b200_embed(const int64_t* ids, const void* table, void* y, int64_t rows,
 int nf4_b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t V, void* stream);
 
 /*
+ * One-shot all-reduce (sum) of a small bf16 tile over peer memory, for the partial outputs of the row-parallel
+ * projections of a tensor-parallel decode step.  In the reference this exchange is an NCCL all-reduce issued by
+ * the torch executor (thunder/executors/torchex.py:2058-2078) after a row-parallel linear
+ * (thunder/distributed/tensor_parallel/row_wise.py:53-80); here every rank stores its tile into a buffer of every
+ * other rank and adds the `world` tiles it received, in rank order, so all ranks get identical bits:
+ *     y = sum_r partial_r (+ residual)          fp32 sums, one rounding to bf16; y may alias residual or partial
+ *   host_buffer_ptrs  HOST array of `world` device addresses: the buffer of rank r as mapped into THIS process
+ *                     (entry `rank` is the caller's own).  Every buffer has buffer_bytes >=
+ *                     nf4_b200_tp_allreduce_buffer_bytes(max numel) bytes, is zero-filled once before its first use
+ *                     and is used by nothing else.  All ranks must issue the same sequence of calls (same numel).
+ *   numel             elements of the tile, a multiple of 8; world <= 8.
+ * The kernel writes to peers with plain stores and reads only its own memory; its waits on the peers' flags are
+ * bounded (0.5 s): a wait that runs out records code 10 in nf4_b200_device_error ([1] block, [2] the rank that did
+ * not arrive) and the call completes with incomplete sums instead of hanging.  Calls on one buffer set must not
+ * overlap on the GPU (one stream).  nf4_b200_tp_allreduce_emulated runs ALL ranks of one exchange on the current
+ * device in a single cooperative launch (arrays indexed by rank): for testing the protocol on one GPU.
+ */
+int64_t nf4_b200_tp_allreduce_buffer_bytes(int64_t max_numel);
+int nf4_b200_tp_allreduce(const void* partial, const void* residual, void* y, int64_t numel, const uint64_t* host_buffer_ptrs,
+                          int64_t buffer_bytes, int rank, int world, void* stream);
+int nf4_b200_tp_allreduce_emulated(const uint64_t* host_partial_ptrs, const uint64_t* host_residual_ptrs,
+                                   const uint64_t* host_y_ptrs, int64_t numel, const uint64_t* host_buffer_ptrs,
+                                   int64_t buffer_bytes, int world, void* stream);
+
+/*
  * Status word of the kernels that wait on in-kernel barriers (the staged GEMV).  Copies 4 words to
  * host memory: [0] first error code (0 = none; GEMV: 1/2/3 = a bounded wait on a full/empty/activation
  * barrier ran out, 4 = unexpected shared-memory window; GEMM: 5/6/7/8 = a bounded wait on the
  * full/empty/weights-ready/accumulator barrier ran out; attention / rotary kernels: 9 = a position outside
- * [0, S_max), then [1] is the batch row and [2] the position), [1] block index, [2] pipeline stage,
+ * [0, S_max), then [1] is the batch row and [2] the position; all-reduce: 10 = a peer's flag did not arrive, [2] is
+ * that peer's rank), [1] block index, [2] pipeline stage,
  * [3] number of waits that ran out.  SYNCHRONISES the device; for tests and diagnosis only.  No
  * counterpart in the reference.
  */

@@ -913,6 +913,7 @@ using namespace nf4;
 namespace nf4 {
 int gemm_read_error(unsigned int* out4);
 int attn_read_error(unsigned int* out4);
+int ar_read_error(unsigned int* out4);
 }
 
 extern "C" int nf4_b200_gemv_decode_fits(int64_t M, int64_t N, int64_t K, int prologue) {
@@ -937,6 +938,11 @@ extern "C" int nf4_b200_device_error(unsigned int* host_out4) {
     if (host_out4[0] == 0) {   // nor a GEMM error: the attention kernels' word
         unsigned int g[4] = {0, 0, 0, 0};
         if (int rc = attn_read_error(g)) return rc;
+        for (int i = 0; i < 4; ++i) host_out4[i] = g[i];
+    }
+    if (host_out4[0] == 0) {   // ... and the tensor-parallel all-reduce's
+        unsigned int g[4] = {0, 0, 0, 0};
+        if (int rc = ar_read_error(g)) return rc;
         for (int i = 0; i < 4; ++i) host_out4[i] = g[i];
     }
     return NF4_OK;

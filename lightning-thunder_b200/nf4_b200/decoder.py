@@ -72,7 +72,7 @@ def _seeded_normal(shape, seed: int, device, std=0.02) -> torch.Tensor:
 class NF4Decoder:
     def __init__(self, cfg: DecoderConfig, batch: int, max_seq: int, device="cuda:0", seed: int = 0, tp_rank: int = 0,
                  tp_size: int = 1, group=None, attn_splits: int | None = None, fused: bool = True, pdl: bool = True,
-                 tensor_core_from: int = 17, prefetch_next: bool = True):
+                 tensor_core_from: int = 17, prefetch_next: bool = True, tp_reduce: str = "oneshot"):
         assert cfg.head_dim == 128, "the attention kernel is written for head_dim 128"
         parallel.check_shardable(cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab, tp_size)
         assert batch <= 16
@@ -138,6 +138,13 @@ class NF4Decoder:
             if tp_size > 1:
                 self.cand = torch.empty((B, 2), device=dev, dtype=torch.float32)
                 self.cand_all = torch.empty((tp_size, B, 2), device=dev, dtype=torch.float32)
+        # the exchange after the row-parallel projections: "oneshot" = this library's all-reduce over peer
+        # memory (x += sum of the ranks' partial tiles in one launch), "nccl" = torch.distributed.all_reduce
+        self.oneshot = None
+        if tp_size > 1 and tp_reduce == "oneshot":
+            from .tp_comm import OneShotAllReduce
+
+            self.oneshot = OneShotAllReduce(group, dev, batch * cfg.d_model)
         self.graph = None
         self.next_pos = 0           # host mirror of the highest position the next step writes (see _guard)
         self.launches_per_step = 0
@@ -187,6 +194,18 @@ class NF4Decoder:
 
     def _all_reduce(self, t):
         torch.distributed.all_reduce(t, group=self.group)
+
+    def _row_parallel(self, inp, w: "NF4Weight", st, next_w=None) -> None:
+        """x <- x + sum over ranks of (inp . W_shard^T): a row-parallel projection and its exchange."""
+        if self.oneshot is not None:
+            self._linear_decode(inp, w, self.part, stream=st, next_w=next_w)
+            self.oneshot(self.part, residual=self.x, out=self.x)
+            self._n += 1
+        else:
+            # rank 0 carries the residual into the sum; the all-reduce completes x = x + inp . W^T
+            self._linear_decode(inp, w, self.part, residual=self.x if self.tp_rank == 0 else None, stream=st, next_w=next_w)
+            self._all_reduce(self.part)
+            self.x, self.part = self.part, self.x          # two swaps per layer: the roles are back after the step
 
     def _linear_decode(self, x, w: NF4Weight, y, residual=None, prologue=0, norm_w=None, swiglu=False, stream=None,
                        next_w: NF4Weight | None = None):
@@ -290,19 +309,13 @@ class NF4Decoder:
                                               self.attn_splits, cfg.rope_theta, self.flags, st), "attn_decode_fused")
             self._n += 1
             if tp:
-                self._linear_decode(self.attn, layer["o"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st,
-                                    next_w=layer["gu"])
-                self._all_reduce(self.part)
-                self.x, self.part = self.part, self.x
+                self._row_parallel(self.attn, layer["o"], st, next_w=layer["gu"])
             else:
                 self._linear_decode(self.attn, layer["o"], self.x, residual=self.x, stream=st, next_w=layer["gu"])
             self._linear_decode(self.x, layer["gu"], self.h, prologue=1, norm_w=layer["norm2"], swiglu=True, stream=st,
                                 next_w=layer["down"])
             if tp:
-                self._linear_decode(self.h, layer["down"], self.part, residual=self.x if self.tp_rank == 0 else None, stream=st,
-                                    next_w=after)
-                self._all_reduce(self.part)
-                self.x, self.part = self.part, self.x
+                self._row_parallel(self.h, layer["down"], st, next_w=after)
             else:
                 self._linear_decode(self.h, layer["down"], self.x, residual=self.x, stream=st, next_w=after)
         self._linear_decode(self.x, self.lm_head, self.logits, prologue=1, norm_w=self.final_norm, stream=st)
