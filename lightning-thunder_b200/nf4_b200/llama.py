@@ -91,6 +91,11 @@ class Attention(nn.Module):
         self.register_buffer("k_cache", torch.zeros(shape), persistent=False)
         self.register_buffer("v_cache", torch.zeros(shape), persistent=False)
 
+    def reset_parameters(self) -> None:
+        """(Re)initialises what the state dict does not carry: an empty cache."""
+        self.k_cache.zero_()
+        self.v_cache.zero_()
+
     def forward(self, x, cos, sin, input_pos, mask):
         B, T, _ = x.shape
         assert B == self.k_cache.shape[0], "the batch must fill the KV cache (max_batch)"
@@ -164,6 +169,25 @@ class LlamaDecoder(nn.Module):
             h = layer(h, cos, sin, input_pos, mask)
         h = self.norm(h[:, -1:, :])
         return self.output(h)
+
+    def _apply(self, fn, recurse=True):
+        """`.to(dtype)` converts floating-point buffers too; the rotary tables stay fp32 whatever the model's type."""
+        super()._apply(fn, recurse)
+        if self.freqs_cos.dtype != torch.float32:
+            dev = self.freqs_cos.device
+            if dev.type == "meta":
+                self.freqs_cos = torch.empty(self.freqs_cos.shape, dtype=torch.float32, device=dev)
+                self.freqs_sin = torch.empty(self.freqs_sin.shape, dtype=torch.float32, device=dev)
+            else:
+                cos, sin = rope_tables(self.args.dim // self.args.n_heads, self.args.max_seq_len, self.args.rope_theta)
+                self.freqs_cos, self.freqs_sin = cos.to(dev), sin.to(dev)
+        return self
+
+    def reset_parameters(self) -> None:
+        """(Re)initialises what the state dict does not carry: the rotary tables."""
+        cos, sin = rope_tables(self.args.dim // self.args.n_heads, self.args.max_seq_len, self.args.rope_theta)
+        self.freqs_cos.copy_(cos)
+        self.freqs_sin.copy_(sin)
 
     def reset_rope_tables(self) -> None:
         """Rebuilds the cos/sin tables in fp32 on the module's device (`.to(dtype)` rounds buffers too)."""

@@ -131,10 +131,14 @@ class NF4LinearQuant4bit(Transform):
         assert w.dtype == expect["dtype"]
         assert w.shape == expect["shape"]
         packed, state = self.quantize_weight(w)
+        # the results go where the module keeps the parameter (the loader copies them in place): when that is
+        # the device they were computed on, they stay there instead of travelling to the source's device and back
+        held = model._overrides_parameters.get(f"{submodule_name}.weight")
+        dst = held.device if held is not None and held.device == packed.device else w.device
         out = dict(state_dict)
-        out["weight"] = packed.to(w.device)
-        out["weight.absmax"] = state.absmax.to(w.device)
-        out["weight.code"] = state.code.to(w.device)
+        out["weight"] = packed.to(dst)
+        out["weight.absmax"] = state.absmax.to(dst)
+        out["weight.code"] = state.code.to(dst)
         return out
 
     # ---- traces -------------------------------------------------------------------------------

