@@ -11,7 +11,8 @@ Transform stack, in order:
   PrunePrologueChecks     drops the per-call re-validation of module members               (thunder/transforms/
                           prune_prologue_checks.py, what thunder/recipes/base.py:103-112 installs)
   CUDAGraphTransform      the computation replays as one CUDA graph                        (thunder/transforms/
-                          cudagraph.py:229-387, what the reduce-overhead plugin installs)
+                          cudagraph.py:229-387, what the reduce-overhead plugin installs; subclassed here only
+                          to make the per-call graph lookup cheaper, see _graph_transform)
 """
 
 from __future__ import annotations
@@ -21,6 +22,41 @@ from torch import nn
 
 from .fusion import NF4DecodeFusion
 from .thunder_executor import NF4LinearQuant4bit, get_nf4_executor, thunder
+
+
+def _graph_transform():
+    """thunder.transforms.cudagraph.CUDAGraphTransform with a cheaper per-call path for modules with hundreds
+    of parameters.  The stock runner (cudagraph.py:137-163) describes dtype, size and stride of EVERY argument on
+    every call to find its graph; here only the arguments that are not static memory (the call's real inputs)
+    are described -- parameters and buffers cannot change their metadata without a new trace -- and a static
+    argument is only compared by identity (a replaced tensor is still copied into the captured one, as upstream)."""
+    from thunder.transforms.cudagraph import CUDAGraphRunner, CUDAGraphTransform, to_arg_descriptor
+
+    class Runner(CUDAGraphRunner):
+        def make_cache_key(self, fn_name, *args):
+            mask = self.make_static_inputs_mask(fn_name, *args)
+            return (fn_name, len(args), to_arg_descriptor(*[a for a, m in zip(args, mask) if not m]))
+
+        def call_cuda_graph(self, fn_name, *args):
+            fn, _ = self.python_callables[fn_name]
+            key = self.make_cache_key(fn_name, *args)
+            entry = self.cuda_graph_cache.get(key)
+            if entry is None:
+                entry = self.build_cuda_graph(fn, args, self.make_static_inputs_mask(fn_name, *args))
+                self.cuda_graph_cache[key] = entry
+            graph, static_inputs, static_outputs = entry
+            for static_input, arg in zip(static_inputs, args):
+                if static_input is not arg and isinstance(static_input, torch.Tensor) and isinstance(arg, torch.Tensor):
+                    static_input.copy_(arg)
+            graph.replay()
+            return static_outputs
+
+    class Transform(CUDAGraphTransform):
+        def __init__(self, *, share_mem_pool: bool = False):
+            super().__init__(share_mem_pool=share_mem_pool)
+            self.cuda_graph_runner = Runner(share_mem_pool=share_mem_pool)
+
+    return Transform()
 
 
 class GreedyStep(nn.Module):
@@ -40,7 +76,6 @@ def compile_decoder(model: nn.Module, *, fuse: bool = True, cuda_graph: bool = T
                     rope_theta: float | None = None, extra_transforms=(), **jit_kwargs):
     """thunder.jit of `model` on the NF4 executor.  Returns the ThunderModule; `.nf4_fusion` is the
     fusion pass (its `fused` / `declined` records say what was rewritten)."""
-    from thunder.transforms.cudagraph import CUDAGraphTransform
     from thunder.transforms.prune_prologue_checks import PrunePrologueChecks
 
     transforms = [NF4LinearQuant4bit()]
@@ -55,7 +90,7 @@ def compile_decoder(model: nn.Module, *, fuse: bool = True, cuda_graph: bool = T
     if prune_checks:
         transforms.append(PrunePrologueChecks())
     if cuda_graph:
-        transforms.append(CUDAGraphTransform())
+        transforms.append(_graph_transform())
     jm = thunder.jit(model, transforms=transforms, executors=(get_nf4_executor(),), **jit_kwargs)
     jm.nf4_fusion = fusion
     return jm
