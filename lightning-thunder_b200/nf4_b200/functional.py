@@ -234,6 +234,21 @@ def linear_nf4(x: torch.Tensor, packed: torch.Tensor, bias, absmax: torch.Tensor
     return out
 
 
+def linear_nf4_input_grad(g: torch.Tensor, packed: torch.Tensor, absmax: torch.Tensor, code: torch.Tensor, blocksize: int,
+                          shape: Sequence[int]) -> torch.Tensor:
+    """dX = g @ dequant(W) for y = x @ dequant(W).T with W of logical `shape` = (N, K): the weight is
+    dequantized to g's dtype by this library's kernel and multiplied by the vendor GEMM (the contraction
+    runs over N, the dimension the packed layout strides over; this is also how the reference's library
+    computes the gradient of a 4-bit linear).  The quantized weight gets no gradient."""
+    N, K = int(shape[0]), int(shape[1])
+    if g.shape[-1] != N:
+        raise RuntimeError(f"linear_nf4_input_grad: g.shape={tuple(g.shape)} does not match weight shape {(N, K)}")
+    _require_cuda(g, "linear_nf4_input_grad input")
+    state = QuantState(absmax=absmax, shape=(N, K), code=code, blocksize=int(blocksize), dtype=g.dtype)
+    w = dequantize_4bit(packed, state)
+    return torch.matmul(g, w)
+
+
 def matmul_4bit(A: torch.Tensor, B: torch.Tensor, quant_state: QuantState, out=None, bias=None) -> torch.Tensor:
     """A @ dequant(B) + bias with B = packed.t() (shape [1, N*K/2]) as the reference passes it
     (thunder/transforms/quantization.py:39); quant_state.shape = (N, K)."""

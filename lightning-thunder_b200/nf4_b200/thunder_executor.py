@@ -40,12 +40,13 @@ from thunder.transforms.utils import add_trace_output, get_checks, trace_with_re
 
 EXECUTOR_NAME = "quant_nf4_b200"
 _executor = None
-nf4_matmul = None   # the Symbol, set by get_nf4_executor()
+nf4_matmul = None       # the Symbol, set by get_nf4_executor()
+nf4_matmul_bwd = None   # its input gradient: g . dequant(W)
 
 
 def get_nf4_executor():
     """Creates (once) the operator executor and its symbol `nf4_b200_matmul`."""
-    global _executor, nf4_matmul
+    global _executor, nf4_matmul, nf4_matmul_bwd
     if _executor is not None:
         return _executor
     ex = thunder.extend.OperatorExecutor(EXECUTOR_NAME, version=0.1)
@@ -60,6 +61,30 @@ def get_nf4_executor():
         return functional.linear_nf4(x, qweight, bias, absmax, quant_map, blocksize, shape)
 
     nf4_matmul = ex.register_operator("nf4_b200_matmul", meta=nf4_matmul_meta, fn=nf4_matmul_impl)
+
+    # Input gradient.  The reference's symbol has no grad rule (training through bnb_matmul_nf4 is unsupported
+    # there); the quantized weight stays frozen, which is what QLoRA needs: adapters added by
+    # thunder.transforms.qlora.LORATransform train, gradients flow through the 4-bit linears.
+    def nf4_matmul_bwd_meta(g, qweight, absmax, quant_map, blocksize, dtype, shape):
+        assert g.shape[-1] == shape[0], f"{g.shape=}, weight {shape=}"
+        return thunder.TensorProxy(like=g, shape=(*g.shape[:-1], shape[1]))
+
+    def nf4_matmul_bwd_impl(g, qweight, absmax, quant_map, blocksize, dtype, shape):
+        return functional.linear_nf4_input_grad(g, qweight, absmax, quant_map, blocksize, shape)
+
+    nf4_matmul_bwd = ex.register_operator("nf4_b200_matmul_bwd", meta=nf4_matmul_bwd_meta, fn=nf4_matmul_bwd_impl)
+
+    def nf4_matmul_grad(x, qweight, bias, absmax, quant_map, blocksize, dtype, shape):
+        from thunder.core.transforms import get_grad, put_grad
+
+        y = nf4_matmul(x, qweight, bias, absmax, quant_map, blocksize, dtype, shape)
+        g = get_grad(y)
+        put_grad(x, nf4_matmul_bwd(g, qweight, absmax, quant_map, blocksize, dtype, shape))
+        if bias is not None and getattr(bias, "requires_grad", False):
+            put_grad(bias, thunder.torch.sum(thunder.torch.reshape(g, (-1, shape[0])), 0))
+        return y
+
+    ex.register_implementation(nf4_matmul, nf4_matmul, checker=lambda *a, **k: True, grad_transform=nf4_matmul_grad)
     _executor = ex
     return ex
 
