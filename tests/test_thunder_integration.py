@@ -323,7 +323,17 @@ def test_cuda_graph_transform_gpu():
     for rows in (1, 40):
         for _ in range(3):      # first call captures, later calls replay with new input values
             x = torch.randn(rows, 512, device="cuda", dtype=torch.bfloat16, generator=g)
-            torch.testing.assert_close(jm_graph(x), jm_plain(x), rtol=1.6e-2, atol=1e-2)
+            y = jm_graph(x)
+            torch.testing.assert_close(y, jm_plain(x), rtol=1.6e-2, atol=1e-2)
+            # and against a third party that shares no kernel with either: the oracle's linears around torch's GELU
+            h = x.cpu()
+            for i in (0, 2):
+                h = _oracle_linear_nf4(h, jm_graph.get_parameter(f"{i}.weight"), m[i].bias.detach().cpu(),
+                                       jm_graph.get_parameter(f"{i}.weight.absmax"), jm_graph.get_parameter(f"{i}.weight.code"),
+                                       64, m[i].weight.shape)
+                if i == 0:
+                    h = torch.nn.functional.gelu(h.float()).to(torch.bfloat16)
+            torch.testing.assert_close(y.float().cpu(), h.float(), rtol=3e-2, atol=3e-2)
     trc = thunder.last_traces(jm_graph)[-1]
     assert any("CUDAGraph" in b.sym.name for b in trc.bound_symbols), [b.sym.name for b in trc.bound_symbols]
     from nf4_b200 import _lib
@@ -455,3 +465,24 @@ def test_plugin_route_through_thunder_compile_cpu(cpu_backend):
     finally:
         if previous is not None:
             thunder.plugins.register_plugin("quantize-int4", previous)
+
+
+@pytest.mark.gpu
+def test_nvtx_ranges_wrap_the_nf4_symbol_gpu():
+    """thunder.dev_utils.nvtx_profile_transform.NvtxProfileTransform (nvtx_profile_transform.py:26-76) composes with
+    the executor: every nf4_b200_matmul call of the execution trace sits between a range push that names it and
+    a pop, and the module still computes the same values."""
+    from thunder.dev_utils.nvtx_profile_transform import NvtxProfileTransform
+
+    ex = get_nf4_executor()
+    m = _mlp(torch.bfloat16, "cuda")
+    jm = thunder.jit(m, transforms=[NF4LinearQuant4bit(), NvtxProfileTransform()], executors=(ex,))
+    plain = thunder.jit(m, transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    x = torch.randn(2, 512, device="cuda", dtype=torch.bfloat16)
+    assert torch.equal(jm(x), plain(x))
+    bs = thunder.last_traces(jm)[-1].bound_symbols
+    at = [i for i, b in enumerate(bs) if b.sym.name == "nf4_b200_matmul"]
+    assert len(at) == 2
+    for i in at:
+        assert bs[i - 1].sym.name == "nvtx_range_push" and "nf4_b200_matmul" in bs[i - 1].args[0]
+        assert bs[i + 1].sym.name == "nvtx_range_pop"
