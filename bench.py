@@ -3,13 +3,20 @@
     python bench.py --gpus N --steps K --warmup W          (N > 1: launched under torch.distributed.run)
     python bench.py --impl reference ...                   the CPU restatement of the same path, host cores
     python bench.py --kernel gemv --N 14336 --K 4096 --M 1 one kernel in isolation (used for ncu captures)
+    python bench.py --workload llama3-8b-prefill --steps 3 the prefill configuration (batch 8 x 2048) through the jitted module
 
-Workload (synthetic, random-init, seeded): N = 1 -> a Llama-3-8B-shaped NF4 decoder, batch 1, a
-512-token random prompt in the KV cache, greedy decode; a "step" is one decode step (one token per
-batch row through all 225 quantized linears + attention over the cache).  N > 1 -> the
-Llama-3-70B-shaped decoder, batch 16, 1024-token prompt, tensor-parallel over the N GPUs (strong
-scaling: the model is fixed).  `value` is tokens/s with the token ids staying on the device;
-`e2e` feeds every step's token ids from pinned host memory and reads the sampled ids back.
+Workload (synthetic, random-init, seeded; no dataset or benchmark suite is involved):
+  N = 1  -> a Llama-3-8B-shaped NF4 decoder, batch 1, a 512-token random prompt in the KV cache, greedy decode; a
+            "step" is one decode step (one token through all 225 quantized linears + attention over the cache).
+            `value` / `e2e` come from the path a user of the reference takes: the nn.Module of nf4_b200.llama
+            jitted by thunder.jit with the NF4 transform, the decode fusion pass and the CUDA-graph transform
+            (`value`: ids stay on the device; `e2e`: ids and position come from pinned host memory every step and
+            the sampled ids are read back).  `engine` holds the same numbers for the decode engine that calls the
+            C ABI directly; `roofline` times the step's GEMV launches alone.
+  N > 1  -> the Llama-3-70B-shaped decoder, batch 16, 1024-token context, tensor-parallel over the N GPUs on the
+            engine (strong scaling: the model is fixed).  Rank 0 first runs the SAME workload on one GPU
+            (`tp1_same_workload_tok_s`), all ranks check a small model against its single-GPU run (`tp_parity`), and
+            the step is timed with the one-shot exchange over peer memory and with NCCL (`exchange`).
 """
 
 from __future__ import annotations
@@ -28,7 +35,6 @@ for _p in (ROOT, os.path.join(ROOT, "lightning-thunder_b200")):
     if _p not in sys.path:
         sys.path.insert(0, _p)
 
-METRIC = "NF4 W4A16 decode tok/s (Llama-3-8B shape); dequant-GEMV HBM GB/s vs 8 TB/s"
 UNIT = "tok/s"
 
 
@@ -154,7 +160,7 @@ def run_reference(args):
     weights = cfg.n_layers * (((cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim) * D + D * cfg.n_heads * cfg.head_dim + 3 * F * D) + cfg.vocab * D
     config = workload_config(cfg.name, batch, prompt_len, args.gpus, weights * 0.5625 / args.gpus)
     line = {
-        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": metric_name(workload, args.gpus), "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": 1000.0 * batch / tok_s, "higher_is_better": True,
         "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": config,
@@ -163,6 +169,8 @@ def run_reference(args):
                                    f"passes ({t_layer * 1e3:.1f} ms each; at most 90 s of them), scaled to all layers + output head"},
         "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        # no whole step runs on the CPU: ms_per_step is one layer's linears scaled to the model
+        "extrapolated": True,
     }
     print(json.dumps(line))
 
@@ -582,6 +590,79 @@ def thunder_decode(cfg, batch, prompt_len, steps, warmup, dev, sampler=None):
     return res
 
 
+def run_prefill(args):
+    """The prefill configuration (batch 8 x 2048 random token ids, causal) through the SAME jitted module: one call
+    processes the whole prompt (16384 activation rows: every linear runs on the tensor-core dequant-GEMM, attention
+    on torch's SDPA through Thunder's own executors, the glue ops eagerly -- neither nvFuser nor Inductor exists
+    here).  Timed as thunder/benchmarks/benchmark_inference.py:200-206, 467-529 times prefill: synchronise,
+    perf_counter around the call; tok/s = batch * prompt / time.  The GEMM's share of the step comes from a
+    profiler pass over one more call."""
+    import torch
+
+    from nf4_b200 import decoder as D
+    from nf4_b200.llama import LlamaArgs, LlamaDecoder
+    from nf4_b200.thunder_decode import GreedyStep, compile_decoder
+
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    cfg = D.LLAMA3_8B
+    B, T = args.B if args.B != 16 else 8, args.prompt or 2048
+    la = LlamaArgs(dim=cfg.d_model, n_layers=cfg.n_layers, n_heads=cfg.n_heads, n_kv_heads=cfg.n_kv_heads, vocab_size=cfg.vocab,
+                   hidden_dim=cfg.ffn, norm_eps=cfg.norm_eps, rope_theta=cfg.rope_theta, max_seq_len=T, max_batch=B)
+    with torch.device(dev):
+        model = LlamaDecoder(la).to(torch.bfloat16).eval().requires_grad_(False)
+    model.init_weights(seed=1)
+    jstep = compile_decoder(GreedyStep(model), cuda_graph=False)
+    gen = torch.Generator().manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab, (B, T), generator=gen).to(dev)
+    pos = torch.arange(T, device=dev)
+    t0 = time.perf_counter()
+    jstep(prompt, pos)
+    torch.cuda.synchronize()
+    first = time.perf_counter() - t0
+    for _ in range(max(1, args.warmup)):
+        jstep(prompt, pos)
+    sampler = ClockSampler(0)
+    sampler.start()
+    times = []
+    for _ in range(max(1, args.steps)):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        jstep(prompt, pos)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    clocks = sampler.stop()
+    sec = statistics.median(times)
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        jstep(prompt, pos)
+        torch.cuda.synchronize()
+    by = {}
+    for e in prof.events():
+        if str(e.device_type).endswith("CUDA"):
+            by[e.name] = by.get(e.name, 0.0) + e.device_time
+    total_us = sum(by.values())
+    gemm_us = sum(v for k, v in by.items() if "gemm_tcgen05" in k)
+    top = sorted(by.items(), key=lambda kv: -kv[1])[:8]
+    weights = cfg.n_layers * (((cfg.n_heads + 2 * cfg.n_kv_heads) * cfg.head_dim) * cfg.d_model + cfg.d_model * cfg.n_heads * cfg.head_dim
+                              + 3 * cfg.ffn * cfg.d_model)
+    flops = 2.0 * B * T * weights
+    peaks, src = measured_peaks()
+    print(json.dumps({
+        "metric": "NF4 W4A16 prefill tok/s (Llama-3-8B shape)", "value": B * T / sec, "unit": UNIT, "n_gpus": 1,
+        "steps": len(times), "warmup": max(1, args.warmup), "ms_per_step": sec * 1e3, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": f"llama3-8b-shape NF4 prefill, batch {B} x {T} tokens, causal", "parallelism": "tp1"},
+        "path": "thunder.jit(model, transforms=[NF4LinearQuant4bit, NF4DecodeFusion (declines: more than 16 rows), PrunePrologueChecks])",
+        "clocks": clocks, "first_call_s": first,
+        "gemm": {"kernel": "gemm_tcgen05_kernel", "share_of_gpu_time": gemm_us / total_us if total_us else None,
+                 "ms": gemm_us / 1e3, "TFLOPs_in_gemm_time": flops / (gemm_us * 1e-6) / 1e12 if gemm_us else None,
+                 "frac_of_" + src: flops / (gemm_us * 1e-6) / 1e12 / peaks["bf16_tflops_sustained" if "bf16_tflops_sustained" in peaks else "bf16_tflops"]
+                 if gemm_us else None},
+        "gpu_time_ms": total_us / 1e3, "top_kernels_ms": [[k[:60], round(v / 1e3, 2)] for k, v in top],
+    }))
+
+
 def tp_parity(world, rank, group, dev):
     """Before timing a tensor-parallel run: the tiny configuration decoded at tp=world by all ranks and at tp=1 on
     rank 0 from the same seeds; logits of the last step and the sampled ids of all steps are compared."""
@@ -741,7 +822,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "llama3-8b", "llama3-70b", "tiny"])
+    ap.add_argument("--workload", default=None, choices=[None, "llama3-8b", "llama3-70b", "tiny", "llama3-8b-prefill"])
     ap.add_argument("--prompt", type=int, default=None, help="override the prompt length")
     ap.add_argument("--no-thunder", action="store_true", help="N = 1: time only the decode engine, not the jitted module")
     ap.add_argument("--no-anchor", action="store_true", help="N > 1: skip the single-GPU run of the same workload")
@@ -762,6 +843,8 @@ def main():
         run_attention(args)
     elif args.kernel:
         run_kernel(args)
+    elif args.workload == "llama3-8b-prefill":
+        run_prefill(args)
     else:
         run_decode(args)
 
