@@ -71,15 +71,20 @@ int nf4_b200_dequantize(const uint8_t* packed, const float* absmax, const float*
  *               call leaves it ready for the next one.  One workspace serves one stream at a time.
  *               Without it the result is the same sums computed by fewer thread blocks.
  * Dispatch: M <= 16 with K % 64 == 0, blocksize 64 and 16-bit dtype -> fused dequant-GEMV
- * (weights streamed once); larger M (bf16) -> tensor-core dequant-GEMM, K split over thread blocks when
- * the weight has few 128-row tiles; anything else (fp32, ragged K, other blocksizes) -> a generic
- * kernel.  fp32 accumulation everywhere.
+ * (weights streamed once); larger M in bf16 -> tensor-core dequant-GEMM, K split over thread blocks when
+ * the weight has few 128-row tiles; larger M in fp16 -> the fused GEMV once per slab of 16 rows; anything
+ * else (fp32, ragged K, other blocksizes) -> a generic kernel.  fp32 accumulation everywhere.
  */
 int nf4_b200_linear(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,
                     const float* code16, int64_t N, int blocksize, const void* bias, void* y, int dtype,
                     void* workspace, int64_t workspace_bytes, void* stream);
 
 int64_t nf4_b200_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int dtype);
+
+/* Which kernel family the calling thread's last nf4_b200_linear call chose (0 before the first call); for tests
+ * and diagnosis.  No counterpart in the reference. */
+enum { NF4_PATH_GEMV = 1, NF4_PATH_GEMM = 2, NF4_PATH_GEMV_SLABS = 3, NF4_PATH_GENERIC = 4 };
+int nf4_b200_last_linear_path(void);
 
 /* The three kernels behind nf4_b200_linear, callable directly (same argument meaning). */
 int nf4_b200_gemv(const void* x, int64_t M, int64_t K, const uint8_t* packed, const float* absmax,

@@ -64,7 +64,11 @@ int gemm_min_m();
 
 using namespace nf4;
 
+static thread_local int g_last_path = 0;
+
 extern "C" int nf4_b200_version(void) { return 100; }
+
+extern "C" int nf4_b200_last_linear_path(void) { return g_last_path; }
 
 extern "C" int nf4_b200_last_error(char* buf, int buflen) {
     const int n = (int)strlen(g_error);
@@ -89,9 +93,20 @@ extern "C" int nf4_b200_linear(const void* x, int64_t M, int64_t K, const uint8_
     if (M == 0 || N == 0) return NF4_OK;
     NF4_REQUIRE(x && packed && absmax && code16 && y, NF4_ERR_ARG, "linear: null pointer");
     const bool gemm_ok = gemm_supported(M, K, N, blocksize, dtype, x, packed, absmax, y);
-    if (!gemm_ok && gemv_supported(M, K, N, blocksize, dtype, x, packed, absmax))
+    if (!gemm_ok && gemv_supported(M, K, N, blocksize, dtype, x, packed, absmax)) {
+        g_last_path = NF4_PATH_GEMV;
         return nf4_b200_gemv(x, M, K, packed, absmax, code16, N, bias, y, dtype, stream);
-    if (gemm_ok)
+    }
+    if (gemm_ok) {
+        g_last_path = NF4_PATH_GEMM;
         return nf4_b200_gemm(x, M, K, packed, absmax, code16, N, bias, y, dtype, workspace, workspace_bytes, stream);
+    }
+    // fp16 with more than 16 rows: the tensor-core kernel is bf16 only; nf4_b200_gemm runs the fused GEMV once per
+    // slab of 16 activation rows instead (the weight streams once per slab, still far ahead of the generic kernel)
+    if (dtype == NF4_F16 && M > 16 && gemv_supported(16, K, N, blocksize, dtype, x, packed, absmax)) {
+        g_last_path = NF4_PATH_GEMV_SLABS;
+        return nf4_b200_gemm(x, M, K, packed, absmax, code16, N, bias, y, dtype, workspace, workspace_bytes, stream);
+    }
+    g_last_path = NF4_PATH_GENERIC;
     return nf4_b200_linear_generic(x, M, K, packed, absmax, code16, N, blocksize, bias, y, dtype, stream);
 }

@@ -224,7 +224,10 @@ extern "C" int nf4_b200_tp_allreduce_emulated(const uint64_t* host_partial_ptrs,
     int blocks = 0;
     if (int rc = ar_plan(numel, world, buffer_bytes, &p, &blocks)) return rc;
     if (int rc = check_device()) return rc;
-    NF4_REQUIRE(blocks * world <= sm_count(), NF4_ERR_LIMIT, "tp_allreduce_emulated: %d blocks x %d ranks do not fit on the device at once", blocks, world);
+    int per_sm = 0;
+    NF4_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, tp_allreduce_kernel, AR_THREADS, 0));
+    NF4_REQUIRE(blocks * world <= sm_count() * per_sm, NF4_ERR_LIMIT,
+                "tp_allreduce_emulated: %d blocks x %d ranks do not fit on the device at once", blocks, world);
     for (int r = 0; r < world; ++r) {
         NF4_REQUIRE(host_buffer_ptrs[r] % 256 == 0 && host_partial_ptrs[r] % 16 == 0 && host_y_ptrs[r] % 16 == 0, NF4_ERR_ALIGN,
                     "tp_allreduce_emulated: rank %d has a misaligned pointer", r);

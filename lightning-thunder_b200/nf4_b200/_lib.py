@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libnf4_b200.so")
 
 NF4_F32, NF4_F16, NF4_BF16 = 0, 1, 2
+PATH_GEMV, PATH_GEMM, PATH_GEMV_SLABS, PATH_GENERIC = 1, 2, 3, 4
 HAS_SWIGLU_HALVES = True   # epilogue 2 of nf4_b200_gemv_decode
 
 _c_i64 = ctypes.c_int64
@@ -23,6 +24,7 @@ _c_ptr = ctypes.c_void_p
 SIGNATURES = {
     "nf4_b200_version": (_c_int, []),
     "nf4_b200_last_error": (_c_int, [ctypes.c_char_p, _c_int]),
+    "nf4_b200_last_linear_path": (_c_int, []),
     "nf4_b200_quantize": (_c_int, [_c_ptr, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "nf4_b200_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr, _c_int, _c_ptr]),
     "nf4_b200_linear": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr, _c_ptr,

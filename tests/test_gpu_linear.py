@@ -183,8 +183,15 @@ def test_gemm_full_prefill_tile_properties(nf4_code_np):
 
 
 def test_fp16_many_rows_uses_gemv_slabs(nf4_code_np):
+    from nf4_b200 import _lib
+
     w = seeded_weight((512, 1024), 77, dtype=torch.float16)
     _check(seeded_act((40, 1024), 78, dtype=torch.float16), w, nf4_code_np)
+    assert _lib.load().nf4_b200_last_linear_path() == _lib.PATH_GEMV_SLABS
+    _check(seeded_act((40, 1024), 78), seeded_weight((512, 1024), 77), nf4_code_np)
+    assert _lib.load().nf4_b200_last_linear_path() == _lib.PATH_GEMM
+    _check(seeded_act((40, 1000), 78, dtype=torch.float16), seeded_weight((512, 1000), 77, dtype=torch.float16), nf4_code_np)
+    assert _lib.load().nf4_b200_last_linear_path() == _lib.PATH_GENERIC       # ragged K
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
