@@ -190,24 +190,32 @@ def run_kernel(args):
     torch.cuda.set_device(0)
     lib = _lib.load()
     N, K, M = args.N, args.K, args.M
-    wbytes = N * K // 2 + N * K // 16
+    # bytes of one weight: codes + fp32 absmax, or (double quantization) codes + 8-bit absmax + one fp32 scale per 256
+    wbytes = N * K // 2 + (N * K // 64 + N * K // 4096 + 1028 if args.dq else N * K // 16)
     nbuf = args.nbuf or max(2, int(4 * 126e6 // wbytes) + 1)     # the rotating set is > 4x the L2
     g = torch.Generator(device="cuda").manual_seed(0)
     ws = []
     for _ in range(nbuf):
         w = (torch.randn((N, K), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
-        ws.append(nf4_b200.quantize_4bit(w))
+        ws.append(nf4_b200.quantize_4bit(w, compress_statistics=args.dq))
         del w
     x = torch.randn((M, K), device="cuda", generator=g).to(torch.bfloat16)
     y = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
     # gemv: the fused GEMV whatever M (up to 16); gemm: the library's dispatch, with its split-K scratch
     need = lib.nf4_b200_linear_workspace_bytes(M, N, K, _lib.NF4_BF16) if args.kernel == "gemm" else 0
     scratch = torch.zeros((max(need, 16),), device="cuda", dtype=torch.uint8)
+    dq_ws = torch.empty((lib.nf4_b200_linear_dq_workspace_bytes(N, K),), device="cuda", dtype=torch.uint8) if args.dq else None
 
     def launch_all():
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
         for p, qs in ws:
-            if args.kernel == "gemv":
+            if args.dq:
+                # double-quantized weight: the fused GEMV expands the 8-bit absmax in its stages (M <= 16), larger M
+                # expands it into dq_ws and runs the tensor-core GEMM
+                rc = lib.nf4_b200_linear_dq(x.data_ptr(), M, K, p.data_ptr(), qs.absmax.data_ptr(), qs.state2.absmax.data_ptr(),
+                                            qs.offset.data_ptr(), qs.state2.code.data_ptr(), qs.code.data_ptr(), N, None,
+                                            y.data_ptr(), _lib.NF4_BF16, dq_ws.data_ptr(), dq_ws.numel(), st)
+            elif args.kernel == "gemv":
                 rc = lib.nf4_b200_gemv(x.data_ptr(), M, K, p.data_ptr(), qs.absmax.data_ptr(), qs.code.data_ptr(), N,
                                        None, y.data_ptr(), _lib.NF4_BF16, st)
             elif args.kernel == "gemm":
@@ -250,7 +258,7 @@ def run_kernel(args):
     else:
         alg = 2 * N * K + wbytes
     peaks, src = measured_peaks()
-    out = {"kernel": args.kernel, "N": N, "K": K, "M": M, "us_per_launch": us, "algorithmic_bytes": alg,
+    out = {"kernel": args.kernel + ("+dq" if args.dq else ""), "N": N, "K": K, "M": M, "us_per_launch": us, "algorithmic_bytes": alg,
            "GBps": alg / us / 1e3, "hbm_frac_of_" + src: alg / us / 1e3 / peaks["hbm_gbs"], "buffers": nbuf}
     if args.kernel == "gemm":
         tf = 2.0 * M * N * K / us / 1e6
@@ -664,8 +672,10 @@ def run_prefill(args):
 
 
 def tp_parity(world, rank, group, dev):
-    """Before timing a tensor-parallel run: the tiny configuration decoded at tp=world by all ranks and at tp=1 on
-    rank 0 from the same seeds; logits of the last step and the sampled ids of all steps are compared."""
+    """Before timing a tensor-parallel run: a small model decoded at tp=world by all ranks and at tp=1 on rank 0
+    from the same seeds and the SAME input ids every step (so one early near-tie cannot send the two runs down
+    different sequences); the logits of every step are compared, and the sampled ids wherever the single-GPU
+    run's best two logits are further apart than the tolerance."""
     import torch
 
     from nf4_b200.decoder import NF4Decoder, tiny_config
@@ -673,18 +683,18 @@ def tp_parity(world, rank, group, dev):
     cfg = tiny_config(n_layers=2, d_model=1024, n_heads=8, n_kv_heads=8, ffn=2048, vocab=4096)
     B, steps = 2, 8
     gen = torch.Generator().manual_seed(7)
-    first = torch.randint(0, cfg.vocab, (B,), generator=gen).to(dev)
+    feed = torch.randint(0, cfg.vocab, (steps, B), generator=gen).to(dev)
 
     def run(tp_rank, tp_size, grp):
         dec = NF4Decoder(cfg, batch=B, max_seq=32, device=dev, seed=3, tp_rank=tp_rank, tp_size=tp_size, group=grp)
-        dec.ids_in.copy_(first)
-        ids = []
-        for _ in range(steps):
+        ids, logits = [], []
+        for t in range(steps):
+            dec.ids_in.copy_(feed[t])
             dec.step()
             ids.append(dec.ids_out.clone())
-            dec.ids_in.copy_(dec.ids_out)
+            logits.append(dec.logits.float().clone())
         torch.cuda.synchronize()
-        return torch.stack(ids), dec.logits.float().clone()
+        return torch.stack(ids), torch.stack(logits)
 
     ids_tp, logits_tp = run(rank, world, group)
     gathered = [torch.empty_like(logits_tp) for _ in range(world)]
@@ -692,11 +702,18 @@ def tp_parity(world, rank, group, dev):
     if rank != 0:
         return None
     ids_1, logits_1 = run(0, 1, None)
-    full = torch.cat(gathered, dim=1)
-    return {"config": "2 layers, d 1024, 8 heads, ffn 2048, vocab 4096, batch 2, 8 greedy steps",
-            "max_abs_logit_diff": float((full - logits_1).abs().max()), "logit_scale": float(logits_1.abs().max()),
-            "tokens_equal": bool(torch.equal(ids_tp, ids_1)), "tolerance": "rtol 1.6e-2 / atol 1e-2 per linear; "
-            "partial sums are rounded to bf16 before the all-reduce"}
+    full = torch.cat(gathered, dim=2)
+    diff = (full - logits_1).abs()
+    tol = 1e-2 + 1.6e-2 * logits_1.abs()
+    top2 = logits_1.topk(2, dim=-1).values
+    clear = (top2[..., 0] - top2[..., 1]) > 2 * (1e-2 + 1.6e-2 * top2[..., 0].abs())
+    return {"config": "2 layers, d 1024, 8 heads, ffn 2048, vocab 4096, batch 2, 8 steps on the same input ids",
+            "max_abs_logit_diff": float(diff.max()), "logit_scale": float(logits_1.abs().max()),
+            "logits_outside_tolerance": float((diff > 3 * tol).float().mean()),
+            "tokens_equal_where_clear": bool(torch.equal(ids_tp[clear], ids_1[clear])), "clear_steps": int(clear.sum()),
+            "tokens_equal": bool(torch.equal(ids_tp, ids_1)),
+            "tolerance": "3 x (atol 1e-2 + rtol 1.6e-2): the per-linear tolerance through a 2-layer model; partial sums are "
+                         "rounded to bf16 before the exchange"}
 
 
 def run_decode(args):
@@ -836,6 +853,7 @@ def main():
     ap.add_argument("--K", type=int, default=4096)
     ap.add_argument("--M", type=int, default=1)
     ap.add_argument("--nbuf", type=int, default=None)
+    ap.add_argument("--dq", action="store_true", help="--kernel gemv/gemm: double-quantized absmax (8-bit, blocks of 256)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
