@@ -63,8 +63,7 @@ constexpr int GM_MAX_WSTAGES = 4;        // packed-weight stages, each GM_WKB K 
 constexpr int GM_WKB = 4;                // K blocks per packed-weight stage: 4 x 32 B = one 128-byte swizzle row
 constexpr int GM_PK_BYTES = GM_BM * 128; // one packed-weight stage
 constexpr int GM_AM_BYTES = GM_BM * 16;  // its absmax: 4 floats per row
-constexpr uint32_t GM_LUT_BASE = 32768;    // byte -> (bf16, bf16): 256 entries x 32 lanes x 4 B = 32 KB at [32K, 64K) of the shared window
-constexpr uint32_t GM_LUT_BYTES = 32768;
+constexpr uint32_t GM_LUT_WINDOW = 65536;  // byte -> (fp32, fp32): 256 entries x 32 lanes x 8 B, 64 KB aligned in the shared window
 constexpr uint32_t GM_LOW_BASE = 2048;     // buffers below the window start here (the dynamic region starts at or below it)
 constexpr int GM_SM_TARGET = 148;        // split K until about one CTA per SM exists
 constexpr unsigned long long GM_WAIT_LIMIT_NS = 200ull * 1000 * 1000;
@@ -152,17 +151,11 @@ __device__ __forceinline__ void gm_tma_2d(uint32_t dst, const CUtensorMap* map, 
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
 }
 
-// table lookup: the packed byte `SEL` of `word` becomes bits 7..14 of the address inside the 32 KB aligned table
-// (entry stride 128 bytes, lane slot 4 bytes: the 32 lanes of a lookup hit 32 different banks); the entry holds
-// the two levels as bf16, widened to fp32 here (a shift and a mask)
+// table lookup: the packed byte `sel` of `word` becomes bits 8..15 of the 64 KB aligned window address
 template <int SEL>
-__device__ __forceinline__ void gm_lookup(uint32_t word, uint32_t table_lane, float& first, float& second) {
-    const uint32_t sh = SEL == 0 ? (word << 7) : (word >> (8 * SEL - 7));
-    const uint32_t addr = (sh & 0x7f80u) | table_lane;
-    uint32_t u;
-    asm("ld.shared.b32 %0, [%1];" : "=r"(u) : "r"(addr));
-    first = __uint_as_float(u << 16);
-    second = __uint_as_float(u & 0xffff0000u);
+__device__ __forceinline__ void gm_lookup(uint32_t word, uint32_t window_lane, float& first, float& second) {
+    const uint32_t addr = __byte_perm(word, window_lane, 0x7604 | (SEL << 4));
+    asm("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(first), "=f"(second) : "r"(addr));
 }
 __device__ __forceinline__ uint32_t gm_scale_pack(float first, float second, float am) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(first * am, second * am);
@@ -269,12 +262,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (warp >= 2 && warp < GM_WPRODUCER) {
-        // byte -> (bf16(code[hi]), bf16(code[lo])) in one 32-bit word (first level in the low half), one copy per
-        // lane (conflict-free lookups): entry e of lane l at table + e * 128 + l * 4
-        const uint32_t mine = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(__ldg(p.code16 + (lane & 15))));
+        // byte -> (float(bf16(code[hi])), float(bf16(code[lo]))), one copy per lane (conflict-free lookups):
+        // entry e of lane l at window + e * 256 + l * 8
+        const float mine = __bfloat162float(__float2bfloat16_rn(__ldg(p.code16 + (lane & 15))));
         for (int e = warp - 2; e < 256; e += GM_DQ_WARPS) {
-            const uint32_t first = __shfl_sync(0xffffffffu, mine, e >> 4), second = __shfl_sync(0xffffffffu, mine, e & 15);
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(GM_LUT_BASE + (uint32_t)(e * 128 + lane * 4)), "r"(first | (second << 16)) : "memory");
+            const float first = __shfl_sync(0xffffffffu, mine, e >> 4), second = __shfl_sync(0xffffffffu, mine, e & 15);
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(GM_LUT_WINDOW + (uint32_t)(e * 256 + lane * 8)), "f"(first), "f"(second) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -362,7 +355,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         const int r = q * 32 + lane;            // weight row inside the tile = TMEM lane
         const int part = (warp - 2) >> 2;       // which quarter of the row's 64-block: packed bytes [8*part, 8*part+8)
         const int grow = n0 + r;
-        const uint32_t window_lane = GM_LUT_BASE | (uint32_t)(lane << 2);
+        const uint32_t window_lane = GM_LUT_WINDOW | (uint32_t)(lane << 3);
         const float* const am_row = p.absmax + (int64_t)(grow < p.N ? grow : 0) * p.KB;
         const bool row_ok = grow < p.N;
         // this thread's 8 bytes of K block j of a packed stage: 16-byte chunk 2j + part/2 at its swizzled place
@@ -569,21 +562,21 @@ static GmEncodeFn gm_encode_fn() {
     return fn;
 }
 
-// Shared-memory map in shared-window addresses: the lookup table owns [32K, 64K); activation stages, packed
-// stages and the barriers are dealt, 1024-byte aligned, first into [GM_LOW_BASE, 32K), then from 64K up.
+// Shared-memory map in shared-window addresses: the lookup table owns [64K, 128K); activation stages, packed
+// stages and the barriers are dealt, 1024-byte aligned, first into [GM_LOW_BASE, 64K), then from 128K up.
 // Returns the dynamic shared memory to request (the region starts at or below GM_LOW_BASE).
 static int gemm_layout(int TM, GemmParams* p) {
-    uint32_t low = GM_LOW_BASE, high = GM_LUT_BASE + GM_LUT_BYTES;
+    uint32_t low = GM_LOW_BASE, high = 2 * GM_LUT_WINDOW;
     auto place = [&](uint32_t bytes) {
         const uint32_t size = (bytes + 1023u) & ~1023u;
         uint32_t addr;
-        if (low + size <= GM_LUT_BASE) { addr = low; low += size; }
+        if (low + size <= GM_LUT_WINDOW) { addr = low; low += size; }
         else { addr = high; high += size; }
         return addr;
     };
-    // activation ring and release unit: 8 stages freed 4 at a time for small tiles, 6 freed in pairs for
-    // 128-row tiles, 4 freed in pairs for 256-row tiles (what fits beside the 32 KB table)
-    const int stages = TM > 128 ? 4 : TM > 64 ? 6 : 8, ru = TM > 128 ? 2 : TM > 64 ? 2 : 4;
+    // activation ring and release unit: 8 stages freed 4 at a time for small tiles, 4 freed in pairs for
+    // 128-row tiles, 3 freed one by one for 256-row tiles (all that fits beside the table)
+    const int stages = TM > 128 ? 3 : TM > 64 ? 4 : 8, ru = TM > 128 ? 1 : TM > 64 ? 2 : 4;
     const int wstages = TM > 128 ? 3 : GM_MAX_WSTAGES;
     if (p) { p->stages = stages; p->wstages = wstages; p->ru_shift = ru == 4 ? 2 : ru == 2 ? 1 : 0; }
     for (int s = 0; s < stages; ++s) {

@@ -112,3 +112,4 @@ def seeded_tensors(model: torch.nn.Module, seed: int, *, device="cuda", std: flo
             part = out[r0:r0 + rows]
             part.copy_(torch.randn(part.shape, generator=g, device=device, dtype=torch.float32).mul_(std))
         yield name, out
+        del out, part            # the consumer's reference is the only one left: freed before the next tensor is drawn
