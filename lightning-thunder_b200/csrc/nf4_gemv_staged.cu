@@ -8,7 +8,7 @@
 //
 // One CTA per SM: 16 compute warps + 1 producer warp.  A stage of the ring holds one tile of 16
 // weight rows x SB 64-blocks (SB <= 32: up to 1 KB of codes per row) plus the SB absmax values
-// of each row.  Compute warp w owns blocks w and w+16 of every stage (K is split over the warps),
+// of each row.  Compute warp w owns blocks 2w and 2w+1 of every stage (K is split over the warps),
 // builds the A fragments of mma.sync.m16n8k16 from the packed bytes with the conflict-free lookup
 // table (see nf4_gemv_common.cuh), multiplies them with the activation fragments (B operand, up to
 // 8 activation rows per column tile) and folds the 4 accumulators of a 64-block into the running
@@ -157,11 +157,6 @@ __device__ __forceinline__ float lds32f(uint32_t addr) {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
@@ -171,25 +166,45 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // One stage of one warp: BPW 64-blocks of a 16-row tile.  Per block: 16 table lookups, 4 chained
 // MMAs per column tile (the chains of different blocks interleave), one scaling by the block's
 // absmax.  HALF: rows 8..15 of the tile do not exist (their fragment registers stay zero).
-// DQ: the stage holds uint8 absmax indices; sc[bi][0/1] are the second-level scales of this lane's two rows
-// (fetched by the caller before it waited for the stage), c256 the shared-memory table, dq_off the offset.
+// The BPW blocks of a warp are adjacent, so their absmax values (or, with double quantization, their uint8
+// indices) come with one load per row.  DQ: sc[0/1] are the second-level scales of this lane's two rows -- a
+// stage never straddles a group of 256 first-level blocks -- fetched by the caller before it waited for the
+// stage; c256 is the shared-memory table, dq_off the offset.
+template <int BPW>
+__device__ __forceinline__ void load_absmax(uint32_t addr, float (&am)[BPW]) {
+    if constexpr (BPW == 2) {
+        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(am[0]), "=f"(am[1]) : "r"(addr));
+    } else {
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(am[0]), "=f"(am[1]), "=f"(am[2]), "=f"(am[3]) : "r"(addr));
+    }
+}
+template <int BPW>
+__device__ __forceinline__ void load_absmax_dq(uint32_t addr, uint32_t c256, float scale, float dq_off, float (&am)[BPW]) {
+    uint32_t bytes;
+    if constexpr (BPW == 2) asm volatile("ld.shared.u16 %0, [%1];" : "=r"(bytes) : "r"(addr));
+    else asm volatile("ld.shared.u32 %0, [%1];" : "=r"(bytes) : "r"(addr));
+#pragma unroll
+    for (int bi = 0; bi < BPW; ++bi) am[bi] = fmaf(lds32f(c256 + 4u * ((bytes >> (8 * bi)) & 0xffu)), scale, dq_off);
+}
+
 template <typename T, int NT, int BPW, bool HALF, bool DQ>
-__device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a_off)[BPW], const uint32_t (&am_off)[BPW],
+__device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a_off)[BPW], uint32_t am_off,
                                               uint32_t rs8, uint32_t as8, uint32_t window_lane,
                                               const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4],
-                                              const float (&sc)[BPW][2], uint32_t c256, float dq_off) {
+                                              const float (&sc)[2], uint32_t c256, float dq_off) {
     uint2 wa[BPW], wb[BPW];
     float ama[BPW], amb[BPW];
 #pragma unroll
     for (int bi = 0; bi < BPW; ++bi) {
         wa[bi] = lds64(sbase + a_off[bi]);
-        if (DQ) ama[bi] = fmaf(lds32f(c256 + 4u * lds8(sbase + am_off[bi])), sc[bi][0], dq_off);
-        else ama[bi] = lds32f(sbase + am_off[bi]);
-        if (!HALF) {
-            wb[bi] = lds64(sbase + a_off[bi] + rs8);
-            if (DQ) amb[bi] = fmaf(lds32f(c256 + 4u * lds8(sbase + am_off[bi] + as8)), sc[bi][1], dq_off);
-            else amb[bi] = lds32f(sbase + am_off[bi] + as8);
-        }
+        if (!HALF) wb[bi] = lds64(sbase + a_off[bi] + rs8);
+    }
+    if (DQ) {
+        load_absmax_dq<BPW>(sbase + am_off, c256, sc[0], dq_off, ama);
+        if (!HALF) load_absmax_dq<BPW>(sbase + am_off + as8, c256, sc[1], dq_off, amb);
+    } else {
+        load_absmax<BPW>(sbase + am_off, ama);
+        if (!HALF) load_absmax<BPW>(sbase + am_off + as8, amb);
     }
     float tmp[BPW][NT][4];
 #pragma unroll
@@ -457,15 +472,15 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     }
 
     const uint32_t window_lane = lut_base | (uint32_t)(lane << 2);
-    // A block this warp does not own (SB < 32) reads a valid block of the stage against all-zero
-    // activation fragments, so every warp always computes BPW blocks.
-    uint32_t a_off[BPW], am_off[BPW];
+    // Warp w owns the adjacent blocks [w * BPW, (w + 1) * BPW) of every stage.  A warp beyond the stage's width
+    // (SB < 32; SB is a multiple of 4, so a warp owns all of its blocks or none) reads the stage's last BPW
+    // blocks against all-zero activation fragments, so every warp always computes BPW blocks.
+    const bool live_warp = warp * BPW < p.SB;
+    const int b0 = min(warp * BPW, p.SB - BPW);
+    uint32_t a_off[BPW];
 #pragma unroll
-    for (int bi = 0; bi < BPW; ++bi) {
-        const int b = min(warp + bi * CW, p.SB - 1);
-        a_off[bi] = (uint32_t)(g * p.RS + b * 32 + q * 8);
-        am_off[bi] = (uint32_t)(16 * p.RS + g * p.AS + b * (DQ ? 1 : 4));
-    }
+    for (int bi = 0; bi < BPW; ++bi) a_off[bi] = (uint32_t)(g * p.RS + (b0 + bi) * 32 + q * 8);
+    const uint32_t am_off = (uint32_t)(16 * p.RS + g * p.AS + b0 * (DQ ? 1 : 4));
     const uint32_t rs8 = 8u * (uint32_t)p.RS, as8 = 8u * (uint32_t)p.AS;
     const uint32_t stage_bytes = (uint32_t)p.stage_bytes;
     const int NS = p.NS;
@@ -480,8 +495,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     auto load_xf = [&](uint32_t (&xf)[BPW][NT][8], int seg) {
 #pragma unroll
         for (int bi = 0; bi < BPW; ++bi) {
-            const int kb = seg * p.SB + warp + bi * CW;
-            const bool live = (warp + bi * CW) < p.SB;
+            const int kb = seg * p.SB + b0 + bi;
+            const bool live = live_warp;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int m = g + nt * 8;
@@ -505,24 +520,21 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     };
 
     // one stage: wait for the box, compute, hand the slot back
-    // DQ: second-level scales of this lane's rows (g, g+8 of the tile starting at row0_) for its blocks of
-    // segment seg_: one scale per 256 consecutive first-level blocks of the flattened weight
-    auto load_scales = [&](float (&sc)[BPW][2], int row0_, int seg_) {
+    // DQ: second-level scales of this lane's rows (g, g+8 of the tile starting at row0_) in segment seg_: one
+    // scale per 256 consecutive first-level blocks of the flattened weight; SB (16 or 32) divides K/64, so the
+    // SB blocks of a row's segment start at a multiple of SB and never straddle a multiple of 256
+    auto load_scales = [&](float (&sc)[2], int row0_, int seg_) {
         if (DQ) {
 #pragma unroll
-            for (int bi = 0; bi < BPW; ++bi) {
-                const int kb = seg_ * p.SB + min(warp + bi * CW, p.SB - 1);
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int row = min(split_gu ? row0_ + g + hh * n_own : row0_ + g + 8 * hh, p.N - 1);
-                    sc[bi][hh] = __ldg(p.scale2 + (((int64_t)row * p.KB + kb) >> 8));
-                }
+            for (int hh = 0; hh < 2; ++hh) {
+                const int row = min(split_gu ? row0_ + g + hh * n_own : row0_ + g + 8 * hh, p.N - 1);
+                sc[hh] = __ldg(p.scale2 + (((int64_t)row * p.KB + seg_ * p.SB) >> 8));
             }
         }
     };
 #define NF4_DO_STAGE(HALF_, XF_, ACC_, ROW0_, SEG_)                                                                 \
     do {                                                                                                           \
-        float sc_[BPW][2];                                                                                         \
+        float sc_[2];                                                                                              \
         load_scales(sc_, ROW0_, SEG_);                                                                             \
         mbar_wait(full0 + slot * 8, parity, abort_flag, 1, stage);                                                  \
         stage_compute<T, NT, BPW, HALF_, DQ>(ring_u32 + slot * stage_bytes, a_off, am_off, rs8, as8, window_lane, XF_, ACC_, sc_, c256, dq_off); \
