@@ -242,6 +242,8 @@ int nf4_b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t V, v
  *                     nf4_b200_tp_allreduce_buffer_bytes(max numel) bytes, is zero-filled once before its first use
  *                     and is used by nothing else.  All ranks must issue the same sequence of calls (same numel).
  *   numel             elements of the tile, a multiple of 8; world <= 8.
+ *   flags             bit 0: programmatic dependent launch (see nf4_b200_gemv_decode): the call may start while the
+ *                     kernel that produces `partial` is finishing, and lets the next kernel of the stream start early.
  * The kernel writes to peers with plain stores and reads only its own memory; its waits on the peers' flags are
  * bounded (0.5 s): a wait that runs out records code 10 in nf4_b200_device_error ([1] block, [2] the rank that did
  * not arrive) and the call completes with incomplete sums instead of hanging.  Calls on one buffer set must not
@@ -250,7 +252,7 @@ int nf4_b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t V, v
  */
 int64_t nf4_b200_tp_allreduce_buffer_bytes(int64_t max_numel);
 int nf4_b200_tp_allreduce(const void* partial, const void* residual, void* y, int64_t numel, const uint64_t* host_buffer_ptrs,
-                          int64_t buffer_bytes, int rank, int world, void* stream);
+                          int64_t buffer_bytes, int rank, int world, int flags, void* stream);
 int nf4_b200_tp_allreduce_emulated(const uint64_t* host_partial_ptrs, const uint64_t* host_residual_ptrs,
                                    const uint64_t* host_y_ptrs, int64_t numel, const uint64_t* host_buffer_ptrs,
                                    int64_t buffer_bytes, int world, void* stream);

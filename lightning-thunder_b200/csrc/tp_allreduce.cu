@@ -52,6 +52,7 @@ struct ArParams {
     int64_t chunk;                        // elements per block (multiple of 8)
     int64_t slot_bytes;                   // bytes between slots
     int emulated;                         // blockIdx.y is the rank
+    int pdl;                              // launched with programmatic stream serialization
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -69,6 +70,10 @@ __device__ __forceinline__ unsigned long long ar_ns() {
 }
 
 __global__ void __launch_bounds__(AR_THREADS) tp_allreduce_kernel(const __grid_constant__ ArParams p) {
+    // Programmatic dependent launch: the next kernel of the stream (a GEMV that starts by streaming weights) may
+    // become resident now; this kernel itself may have started while its predecessor (the GEMV that writes
+    // `partial`) was still running and waits for it below, before it reads anything the predecessor wrote.
+    if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int b = blockIdx.x;
     const int rank = p.emulated ? (int)blockIdx.y : p.rank;
     const int slot = p.emulated ? rank : 0;
@@ -82,6 +87,7 @@ __global__ void __launch_bounds__(AR_THREADS) tp_allreduce_kernel(const __grid_c
         s_epoch = e;
     }
     __syncthreads();
+    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t epoch = s_epoch;
     const int set = (int)(epoch & 1u);
     const int64_t e0 = (int64_t)b * p.chunk;
@@ -193,7 +199,8 @@ extern "C" int64_t nf4_b200_tp_allreduce_buffer_bytes(int64_t max_numel) {
 }
 
 extern "C" int nf4_b200_tp_allreduce(const void* partial, const void* residual, void* y, int64_t numel,
-                                     const uint64_t* host_buffer_ptrs, int64_t buffer_bytes, int rank, int world, void* stream) {
+                                     const uint64_t* host_buffer_ptrs, int64_t buffer_bytes, int rank, int world, int flags,
+                                     void* stream) {
     NF4_REQUIRE(partial && y && host_buffer_ptrs, NF4_ERR_ARG, "tp_allreduce: null pointer");
     NF4_REQUIRE(rank >= 0 && rank < world, NF4_ERR_ARG, "tp_allreduce: rank %d of %d", rank, world);
     NF4_REQUIRE(reinterpret_cast<uintptr_t>(partial) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0 &&
@@ -211,8 +218,17 @@ extern "C" int nf4_b200_tp_allreduce(const void* partial, const void* residual, 
     p.y[0] = static_cast<bf16*>(y);
     p.rank = rank;
     p.emulated = 0;
-    tp_allreduce_kernel<<<blocks, AR_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
-    NF4_CUDA_TRY(cudaGetLastError());
+    p.pdl = flags & 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(AR_THREADS);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;
+    NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, tp_allreduce_kernel, p));
     return NF4_OK;
 }
 

@@ -66,7 +66,7 @@ SIGNATURES = {
     "nf4_b200_embed": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr]),
     "nf4_b200_argmax": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_ptr]),
     "nf4_b200_tp_allreduce_buffer_bytes": (_c_i64, [_c_i64]),
-    "nf4_b200_tp_allreduce": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr]),
+    "nf4_b200_tp_allreduce": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_i64, _c_int, _c_int, _c_int, _c_ptr]),
     "nf4_b200_tp_allreduce_emulated": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_i64, _c_int, _c_ptr]),
 }
 

@@ -199,7 +199,7 @@ class NF4Decoder:
         """x <- x + sum over ranks of (inp . W_shard^T): a row-parallel projection and its exchange."""
         if self.oneshot is not None:
             self._linear_decode(inp, w, self.part, stream=st, next_w=next_w)
-            self.oneshot(self.part, residual=self.x, out=self.x)
+            self.oneshot(self.part, residual=self.x, out=self.x, pdl=bool(self.flags & 1))
             self._n += 1
         else:
             # rank 0 carries the residual into the sum; the all-reduce completes x = x + inp . W^T

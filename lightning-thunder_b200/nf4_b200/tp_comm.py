@@ -41,7 +41,7 @@ class OneShotAllReduce:
         self.ptrs = (ctypes.c_uint64 * self.world)(*ptrs)
         dist.barrier(group)          # every rank has zeroed its flags before anybody's first store arrives
 
-    def __call__(self, partial: torch.Tensor, residual=None, out=None) -> torch.Tensor:
+    def __call__(self, partial: torch.Tensor, residual=None, out=None, pdl: bool = False) -> torch.Tensor:
         n = partial.numel()
         if partial.dtype != torch.bfloat16 or not partial.is_contiguous() or n > self.max_numel or n % 8:
             raise ValueError(f"OneShotAllReduce: contiguous bf16 tiles of up to {self.max_numel} elements (multiple of 8)")
@@ -49,6 +49,6 @@ class OneShotAllReduce:
             out = torch.empty_like(partial)
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check(self.lib.nf4_b200_tp_allreduce(partial.data_ptr(), residual.data_ptr() if residual is not None else None,
-                                                  out.data_ptr(), n, self.ptrs, self.nbytes, self.rank, self.world, st),
+                                                  out.data_ptr(), n, self.ptrs, self.nbytes, self.rank, self.world, 1 if pdl else 0, st),
                    "nf4_b200_tp_allreduce")
         return out
