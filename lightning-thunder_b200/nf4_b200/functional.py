@@ -420,6 +420,35 @@ def silu_mul(gate_up: torch.Tensor, F: int, interleaved: bool) -> torch.Tensor:
     return out
 
 
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """table[ids] for a bf16 table [vocab, D] and int64 ids of any shape (one launch, 16-byte row copies)."""
+    _require_cuda(table, "embedding table")
+    if table.dtype != torch.bfloat16 or ids.dtype != torch.int64 or table.dim() != 2 or not table.is_contiguous():
+        raise ValueError("embedding: contiguous bf16 table [vocab, D] and int64 ids")
+    flat = ids.reshape(-1).contiguous()
+    with torch.cuda.device(table.device):
+        out = torch.empty((*ids.shape, table.shape[1]), dtype=table.dtype, device=table.device)
+        _lib.check(_lib.load().nf4_b200_embed(flat.data_ptr(), table.data_ptr(), out.data_ptr(), flat.numel(), table.shape[1],
+                                              table.shape[0], _stream_ptr(table.device)), "nf4_b200_embed")
+    return out
+
+
+def argmax_last(logits: torch.Tensor, keepdim: bool = False) -> torch.Tensor:
+    """argmax over the last dimension of a contiguous bf16 tensor; the first maximum wins (as torch.argmax)."""
+    _require_cuda(logits, "argmax input")
+    if logits.dtype != torch.bfloat16:
+        raise ValueError("argmax_last: bf16 only")
+    x2 = logits.reshape(-1, logits.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    with torch.cuda.device(logits.device):
+        out = torch.empty((x2.shape[0],), dtype=torch.int64, device=logits.device)
+        _lib.check(_lib.load().nf4_b200_argmax(x2.data_ptr(), out.data_ptr(), x2.shape[0], x2.shape[1], _stream_ptr(logits.device)),
+                   "nf4_b200_argmax")
+    shape = (*logits.shape[:-1], 1) if keepdim else logits.shape[:-1]
+    return out.view(shape)
+
+
 def swiglu_halves_available() -> bool:
     """Whether the fused GEMV has the SwiGLU epilogue over [gate rows; up rows] (epilogue 2)."""
     return _lib.HAS_SWIGLU_HALVES

@@ -85,6 +85,34 @@ def get_nf4_executor():
         return y
 
     ex.register_implementation(nf4_matmul, nf4_matmul, checker=lambda *a, **k: True, grad_transform=nf4_matmul_grad)
+
+    # The two torch-level ops at the ends of a decode step are claimed too when they have the form this
+    # library's kernels take (thunder/extend/__init__.py:264-281: an implementation + a checker; everything the
+    # checkers refuse stays with the executors behind this one): the token embedding lookup and the greedy
+    # argmax over the vocabulary.
+    def _on_cuda(p):
+        return getattr(getattr(p, "device", None), "devicetype", None) == thunder.devices.DeviceType.CUDA
+
+    def embedding_checker(a, weight, padding_idx=None, max_norm=None, norm_type=2.0, scale_grad_by_freq=False, sparse=False):
+        return (_on_cuda(weight) and _on_cuda(a) and weight.dtype == thunder.dtypes.bfloat16 and a.dtype == thunder.dtypes.int64
+                and weight.ndim == 2 and weight.shape[1] % 8 == 0 and padding_idx is None and max_norm is None
+                and not getattr(weight, "requires_grad", False))
+
+    def embedding_impl(a, weight, padding_idx=None, max_norm=None, norm_type=2.0, scale_grad_by_freq=False, sparse=False):
+        return functional.embedding(a, weight)
+
+    nf4_embedding = ex.register_operator("nf4_b200_embedding", like=thunder.torch.embedding, fn=embedding_impl)
+    ex.register_implementation(thunder.torch.embedding, nf4_embedding, checker=embedding_checker)
+
+    def argmax_checker(a, dim=None, keepdim=False):
+        return (_on_cuda(a) and a.dtype == thunder.dtypes.bfloat16 and a.ndim >= 1 and dim is not None
+                and (dim == -1 or dim == a.ndim - 1))
+
+    def argmax_impl(a, dim=None, keepdim=False):
+        return functional.argmax_last(a, bool(keepdim))
+
+    nf4_argmax = ex.register_operator("nf4_b200_argmax", like=thunder.torch.argmax, fn=argmax_impl)
+    ex.register_implementation(thunder.torch.argmax, nf4_argmax, checker=argmax_checker)
     _executor = ex
     return ex
 

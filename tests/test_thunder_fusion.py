@@ -166,6 +166,9 @@ def test_fused_decode_on_kernels_matches_oracle_backend(monkeypatch, B):
     assert fusion.fused["attn"] == args.n_layers and not fusion.declined
     names = _names(thunder.last_traces(jg)[-1])
     assert any("CUDAGraph" in n for n in names)
+    # the embedding lookup was claimed by this executor too (bf16 table on CUDA), inside the captured region
+    region = [b for b in thunder.last_traces(jg)[-1].bound_symbols if "CUDAGraph" in b.sym.name][0]
+    assert "nf4_b200_embedding" in [s.sym.name for s in region.subsymbols]
     assert _lib.device_error()[0] == 0
     monkeypatch.setattr(functional, "quantize_4bit", _oracle_quantize_4bit)
     monkeypatch.setattr(functional, "linear_nf4", _oracle_linear_nf4)
@@ -174,3 +177,26 @@ def test_fused_decode_on_kernels_matches_oracle_backend(monkeypatch, B):
     want = _decode(jc, 6, B, args.vocab_size)
     torch.testing.assert_close(got, want, rtol=5e-2, atol=5e-2)
     assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.9
+
+
+@pytest.mark.gpu
+def test_greedy_step_claims_embedding_and_argmax_gpu():
+    """GreedyStep (model + argmax) jitted by compile_decoder: token embedding and greedy argmax run on this
+    library's kernels (claimed through register_implementation + checker), and the sampled ids equal torch's
+    argmax over the logits of the same module without the final op."""
+    from nf4_b200.thunder_decode import GreedyStep, compile_decoder
+
+    args = tiny_args(dim=512, n_heads=4, n_kv_heads=2, hidden_dim=1024, vocab_size=2048, max_seq_len=64, max_batch=2)
+    js = compile_decoder(GreedyStep(build(args, "cuda")))
+    jl = compile_decoder(build(args, "cuda"))
+    g = torch.Generator().manual_seed(5)
+    for p in range(4):
+        tok = torch.randint(0, args.vocab_size, (2, 1), generator=g).cuda()
+        pos = torch.tensor([p], device="cuda")
+        ids = js(tok, pos).clone()
+        logits = jl(tok, pos)
+        assert ids.shape == (2, 1) and ids.dtype == torch.int64
+        assert torch.equal(ids, logits[:, -1, :].float().argmax(-1, keepdim=True))
+    region = [b for b in thunder.last_traces(js)[-1].bound_symbols if "CUDAGraph" in b.sym.name][0]
+    inner = [s.sym.name for s in region.subsymbols]
+    assert "nf4_b200_embedding" in inner and "nf4_b200_argmax" in inner
