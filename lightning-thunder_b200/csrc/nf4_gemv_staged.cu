@@ -545,21 +545,24 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     } while (0)
 
     // end of a group: the CW partial sums of every output meet in shared memory (fixed order)
-    auto finish_group = [&](int tile0, int nt_here) {
-        float* const mine = part + warp * (TG * Mc * 16);   // layout part[warp][j][m][16 rows]
+    // (the exchange buffer holds at most 4 tiles: a group of 8 is finished in two halves, JB = first tile of the half)
+    constexpr int TGF = TG > 4 ? 4 : TG;
+    auto finish_tiles = [&](int tile0, int nt_here, auto JB) {
+        constexpr int jb = decltype(JB)::value;
+        float* const mine = part + warp * (TGF * Mc * 16);   // layout part[warp][j][m][16 rows]
 #pragma unroll
-        for (int j = 0; j < TG; ++j) {
+        for (int j = 0; j < TGF; ++j) {
             if (j < nt_here) {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     const int m = nt * 8 + 2 * q;
                     if (m < Mc) {
-                        mine[(j * Mc + m) * 16 + g] = acc[j][nt][0];
-                        mine[(j * Mc + m) * 16 + g + 8] = acc[j][nt][2];
+                        mine[(j * Mc + m) * 16 + g] = acc[jb + j][nt][0];
+                        mine[(j * Mc + m) * 16 + g + 8] = acc[jb + j][nt][2];
                     }
                     if (m + 1 < Mc) {
-                        mine[(j * Mc + m + 1) * 16 + g] = acc[j][nt][1];
-                        mine[(j * Mc + m + 1) * 16 + g + 8] = acc[j][nt][3];
+                        mine[(j * Mc + m + 1) * 16 + g] = acc[jb + j][nt][1];
+                        mine[(j * Mc + m + 1) * 16 + g + 8] = acc[jb + j][nt][3];
                     }
                 }
             }
@@ -581,8 +584,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                     const int idx = jm * 16 + 2 * pr;
 #pragma unroll
                     for (int w = 0; w < CW; ++w) {
-                        sg += part[w * (TG * Mc * 16) + idx];
-                        su += part[w * (TG * Mc * 16) + idx + 1];
+                        sg += part[w * (TGF * Mc * 16) + idx];
+                        su += part[w * (TGF * Mc * 16) + idx + 1];
                     }
                     const float gt = Elem<T>::to_f32(Elem<T>::from_f32(sg));
                     const float up = Elem<T>::to_f32(Elem<T>::from_f32(su));
@@ -606,8 +609,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                     const int idx = jm * 16 + pr;
 #pragma unroll
                     for (int w = 0; w < CW; ++w) {
-                        sg += part[w * (TG * Mc * 16) + idx];
-                        su += part[w * (TG * Mc * 16) + idx + 8];
+                        sg += part[w * (TGF * Mc * 16) + idx];
+                        su += part[w * (TGF * Mc * 16) + idx + 8];
                     }
                     const float gt = Elem<T>::to_f32(Elem<T>::from_f32(sg));
                     const float up = Elem<T>::to_f32(Elem<T>::from_f32(su));
@@ -627,13 +630,20 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             if (grow < r1) {
                 float sum = 0.0f;
 #pragma unroll
-                for (int w = 0; w < CW; ++w) sum += part[w * (TG * Mc * 16) + o];
+                for (int w = 0; w < CW; ++w) sum += part[w * (TGF * Mc * 16) + o];
                 if (p.bias) sum += Elem<T>::to_f32(static_cast<const T*>(p.bias)[grow]);
                 if (p.residual) sum += Elem<T>::to_f32(static_cast<const T*>(p.residual)[(int64_t)m * p.N + grow]);
                 static_cast<T*>(p.y)[(int64_t)m * p.N + grow] = Elem<T>::from_f32(sum);
             }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    };
+
+    auto finish_group = [&](int tile0, int nt_here) {
+        finish_tiles(tile0, min(nt_here, TGF), std::integral_constant<int, 0>());
+        if constexpr (TG > 4) {
+            if (nt_here > 4) finish_tiles(tile0 + 4, nt_here - 4, std::integral_constant<int, 4>());
+        }
     };
 
     auto zero_acc = [&]() {
@@ -836,11 +846,14 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         const int v = atoi(env);
         if (v == 8 || v == 16) CW = v;
     }
+    // (two column tiles on 8 warps whose activations come from L2: groups of 8 tiles when the CTA has that many,
+    // so the 16 x K activations are fetched half as often)
     int TG = (NT == 1 || CW == 8) ? 4 : 2;
+    if (NT == 2 && CW == 8 && tiles > 4) TG = 8;
     while (TG > 1 && TG / 2 >= tiles) TG /= 2;
     if (const char* env = getenv("NF4_GEMV_TG")) {
         const int v = atoi(env);
-        if (v == 1 || v == 2 || (v == 4 && (NT == 1 || CW == 8))) TG = v;
+        if (v == 1 || v == 2 || (v == 4 && (NT == 1 || CW == 8)) || (v == 8 && NT == 2 && CW == 8)) TG = v;
     }
 
     StagedParams p;
@@ -876,7 +889,7 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     p.off_bars = 0;
     p.off_c256 = 256;
     p.off_part = dq ? 256 + 1024 : 256;
-    const int part_bytes = CW * TG * M * 16 * 4;
+    const int part_bytes = CW * (TG > 4 ? 4 : TG) * M * 16 * 4;
     p.off_x = (p.off_part + part_bytes + 127) & ~127;
     if (p.off_x > low_cap) return -1;
     p.x_staged = ((int64_t)p.off_x + (int64_t)M * p.x_stride <= low_cap) ? 1 : 0;
@@ -906,6 +919,7 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         if (TG == 2) NF4_SG(1, 2);
         NF4_SG(1, 1);
     } else {
+        if (TG == 8) return launch_staged<T, 2, 8, 8>(p, grid, stream);
         if (TG == 4) return launch_staged<T, 2, 4, 8>(p, grid, stream);
         if (TG == 2) NF4_SG(2, 2);
         NF4_SG(2, 1);
