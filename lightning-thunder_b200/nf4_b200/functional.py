@@ -331,11 +331,12 @@ def gemv_decode_fits(M: int, N: int, K: int, prologue: int) -> bool:
 
 def gemv_decode(x: torch.Tensor, packed: torch.Tensor, absmax: torch.Tensor, code: torch.Tensor, N: int, K: int, *,
                 prologue: int = 0, norm_w=None, eps: float = 0.0, epilogue: int = 0, residual=None, out=None,
-                pdl: bool = False) -> torch.Tensor:
+                pdl: bool = False, next_weight=None) -> torch.Tensor:
     """y = prologue(x) @ dequant(W[N, K]).T (+ residual), bf16, at most 16 activation rows.
     prologue 1: RMSNorm of x with weight norm_w; 2: x is [M, 2K] = [gate | up] and becomes silu(gate) * up.
     epilogue 1 / 2: W's rows are (gate_i, up_i) pairs / W is [gate rows; up rows], and y [M, N/2] =
-    silu(x.gate_i) * (x.up_i)."""
+    silu(x.gate_i) * (x.up_i).  next_weight = (packed, absmax, N, K) of the weight the NEXT launch on this stream
+    streams: its head is pulled into L2 while this launch drains (a pure prefetch)."""
     _require_cuda(x, "gemv_decode input")
     if x.dtype != torch.bfloat16:
         raise ValueError("gemv_decode: bf16 activations only")
@@ -350,6 +351,10 @@ def gemv_decode(x: torch.Tensor, packed: torch.Tensor, absmax: torch.Tensor, cod
     with torch.cuda.device(x.device):
         if out is None:
             out = torch.empty((*x.shape[:-1], n_out), dtype=x.dtype, device=x.device)
+        if next_weight is not None:
+            nw_p, nw_a, nw_n, nw_k = next_weight
+            _lib.check(_lib.load().nf4_b200_gemv_decode_next_weight(nw_p.data_ptr(), nw_a.data_ptr(), int(nw_n), int(nw_k)),
+                       "nf4_b200_gemv_decode_next_weight")
         _lib.check(
             _lib.load().nf4_b200_gemv_decode(x2.data_ptr(), M, K, packed.data_ptr(), absmax.data_ptr(), code.data_ptr(), N,
                                              residual.data_ptr() if residual is not None else None, out.data_ptr(),

@@ -81,7 +81,7 @@ def _rmsnorm_rows(x2, norm_w, eps):
     return torch.nn.functional.rms_norm(x2, (x2.shape[-1],), norm_w, eps)
 
 
-def _gemv(x2, packed, absmax, code, N, K, *, norm_w=None, eps=0.0, epilogue=0, residual=None, pdl=True):
+def _gemv(x2, packed, absmax, code, N, K, *, norm_w=None, eps=0.0, epilogue=0, residual=None, pdl=True, next_weight=None):
     """Fused GEMV with an optional RMSNorm prologue; when the activations do not fit beside the kernel's
     tables the norm runs as its own op first."""
     F = functional
@@ -91,7 +91,7 @@ def _gemv(x2, packed, absmax, code, N, K, *, norm_w=None, eps=0.0, epilogue=0, r
         x2 = _rmsnorm_rows(x2, norm_w, eps)
         prologue, norm_w = F.PROLOGUE_NONE, None
     return F.gemv_decode(x2, packed, absmax, code, N, K, prologue=prologue, norm_w=norm_w, eps=eps, epilogue=epilogue,
-                         residual=residual, pdl=pdl)
+                         residual=residual, pdl=pdl, next_weight=next_weight)
 
 
 def _positions_impl(input_pos, B):
@@ -103,8 +103,9 @@ def _attn_block_impl(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cac
     D = x.shape[-1]
     B = x.numel() // D
     x2 = x.reshape(B, D)
+    # (the weight the next GEMV streams is hinted to each GEMV: the attention launch in between reads no weights)
     qkv = _gemv(x2, _span((wq, wk, wv), "q/k/v weight"), _span((aq, ak, av), "q/k/v absmax"), code,
-                (Hq + 2 * Hkv) * HEAD_DIM, D, norm_w=norm_w, eps=eps)
+                (Hq + 2 * Hkv) * HEAD_DIM, D, norm_w=norm_w, eps=eps, next_weight=(wo, ao, D, Hq * HEAD_DIM))
     att = F.attn_decode_fused(qkv, positions, k_cache, v_cache, Hq, Hkv, theta, pdl=True)
     y = _gemv(att, wo, ao, code, D, Hq * HEAD_DIM, residual=x2)
     return y.view(x.shape)
@@ -117,7 +118,8 @@ def _mlp_block_impl(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim):
     h2 = h.reshape(B, D)
     packed, absmax = _span((w1, w3), "gate/up weight"), _span((a1, a3), "gate/up absmax")
     if F.gemv_decode_fits(B, 2 * Fdim, D, F.PROLOGUE_RMSNORM) and F.swiglu_halves_available():
-        act = _gemv(h2, packed, absmax, code, 2 * Fdim, D, norm_w=norm_w, eps=eps, epilogue=F.EPILOGUE_SWIGLU_HALVES)
+        act = _gemv(h2, packed, absmax, code, 2 * Fdim, D, norm_w=norm_w, eps=eps, epilogue=F.EPILOGUE_SWIGLU_HALVES,
+                    next_weight=(w2, a2, D, Fdim))
     else:
         gu = _gemv(h2, packed, absmax, code, 2 * Fdim, D, norm_w=norm_w, eps=eps)
         act = F.silu_mul(gu, Fdim, interleaved=False)

@@ -41,7 +41,7 @@ def _bf(t):
 
 
 def cpu_gemv_decode(x, packed, absmax, code, N, K, *, prologue=0, norm_w=None, eps=0.0, epilogue=0, residual=None, out=None,
-                    pdl=False):
+                    pdl=False, next_weight=None):
     import oracle
 
     in_cols = 2 * K if prologue == 2 else K
