@@ -88,9 +88,9 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------
 
 # DRAM traffic of the fused dequant-GEMV relative to its algorithmic bytes, from one ncu capture of the kernel
-# (N=32064, K=4096, M=1: 73.95 MB read + 0.93 MB written against 73.95 MB algorithmic); the kernel streams
+# (N=32064, K=4096, M=1: 73.95 MB read + 1.05 MB written against 73.95 MB algorithmic); the kernel streams
 # every weight byte exactly once, so traffic grows in proportion to N*K.
-NCU_TRAFFIC_RATIO = 74.875 / 73.948
+NCU_TRAFFIC_RATIO = 75.006 / 73.948
 
 
 def workload_config(name: str, batch: int, prompt_len: int, world: int, step_bytes: float) -> dict:
@@ -805,7 +805,7 @@ def run_decode(args):
                      "frac": achieved / peaks["hbm_gbs"], "peak_source": src,
                      "traffic": NCU_TRAFFIC_RATIO * sum(gemv_bytes) / len(gemv_bytes),
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch at 32064x4096, M=1 "
-                                       "(74.88 MB for 73.95 MB algorithmic), scaled by algorithmic bytes",
+                                       "(75.01 MB for 73.95 MB algorithmic), scaled by algorithmic bytes",
                      "kernel": "gemv_staged_kernel (fused NF4 dequant-GEMV)", "launches_per_step": len(gemv_bytes),
                      "avg_launch_us": chain_us / len(gemv_bytes), "algorithmic_bytes_per_launch": sum(gemv_bytes) / len(gemv_bytes),
                      "frac_of_8TBps": achieved / 8000.0,
