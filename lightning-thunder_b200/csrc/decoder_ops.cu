@@ -48,16 +48,20 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const bf16* __restrict__ x
 // Such a row writes nothing to the cache and attends to nothing (its output is zero).
 __device__ unsigned int g_attn_error[4];
 
-__device__ __forceinline__ bool position_ok(int pos, int S_max, int b) {
-    if (pos >= 0 && pos < S_max) return true;
-    if (threadIdx.x == 0) {
-        if (atomicCAS(&g_attn_error[0], 0u, 9u) == 0u) {
-            g_attn_error[1] = (unsigned)b;
-            g_attn_error[2] = (unsigned)pos;
-        }
-        atomicAdd(&g_attn_error[3], 1u);
+__device__ __forceinline__ bool position_in_range(int pos, int S_max) { return (unsigned)pos < (unsigned)S_max; }
+
+__device__ __noinline__ void report_bad_position(int b, int pos) {
+    if (atomicCAS(&g_attn_error[0], 0u, 9u) == 0u) {
+        g_attn_error[1] = (unsigned)b;
+        g_attn_error[2] = (unsigned)pos;
     }
-    return false;
+    atomicAdd(&g_attn_error[3], 1u);
+}
+
+__device__ __forceinline__ bool position_ok(int pos, int S_max, int b) {
+    const bool ok = position_in_range(pos, S_max);
+    if (!ok && threadIdx.x == 0) report_bad_position(b, pos);
+    return ok;
 }
 
 // ---- rotary embedding on q and k (interleaved pairs) + append k, v to the cache ---------------
@@ -370,7 +374,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int hk = blockIdx.x, b = blockIdx.y, sp = blockIdx.z;
     const int pos = positions[b];
-    const bool pos_ok = position_ok(pos, S_max, b);
+    const bool pos_ok = position_in_range(pos, S_max);    // reported beside the arrival counter, off the start-up path
     const int len = pos_ok ? pos + 1 : 0;
     const int chunk = (len + nsplit - 1) / nsplit;
     const int s_begin = sp * chunk;
@@ -449,6 +453,7 @@ __global__ void __launch_bounds__(128) attn_fused_kernel(const bf16* __restrict_
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
+        if (!pos_ok) report_bad_position(b, pos);
         const unsigned int old = atomicAdd(&counters[b * Hkv + hk], 1u);
         s_last = (old == (unsigned int)(nsplit - 1)) ? 1 : 0;
     }

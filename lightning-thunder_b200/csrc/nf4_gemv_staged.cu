@@ -252,7 +252,9 @@ __device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a
         }
 }
 
-template <typename T, int NT, int TG, int CW, bool DQ>
+// GU: epilogue 2 (SwiGLU over [gate rows; up rows]).  A template flag, not a run-time test: the extra producer
+// and finishing code measurably slowed the plain kernel (about 3 % of a decode step) when it was compiled in.
+template <typename T, int NT, int TG, int CW, bool DQ, bool GU>
 __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __grid_constant__ StagedParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     constexpr int BPW = 32 / CW;          // 64-blocks of a stage per warp
@@ -276,7 +278,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     // most one half tile
     // (epilogue 2: the halves count gate rows; every half is a full tile with its 8 up rows)
     const int bid = (int)blockIdx.x;
-    const bool split_gu = p.epilogue == 2;
+    constexpr bool split_gu = GU;
     const int n_own = split_gu ? (p.N >> 1) : p.N;      // rows that are dealt out
     const int tile_rows = split_gu ? 8 : 16;            // ... and how many of them one tile covers
     const int h0 = bid * p.h_base + min(bid, p.h_rem);
@@ -328,7 +330,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                         const uint32_t fullb = full0 + slot * 8;
                         const uint32_t sbase = ring_u32 + (uint32_t)slot * (uint32_t)p.stage_bytes;
                         mbar_expect_tx(fullb, (uint32_t)(half ? 8 : 16) * (uint32_t)(p.RS + p.AS));
-                        if (split_gu) {
+                        if constexpr (split_gu) {
                             // rows 0..7 of the tile: gate rows row0.., rows 8..15: the up rows of the same outputs
                             tma_load_2d(sbase, &p.wmap8, seg * p.SB * 4, row0, fullb);
                             tma_load_2d(sbase + 8 * p.RS, &p.wmap8, seg * p.SB * 4, n_own + row0, fullb);
@@ -545,24 +547,21 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     } while (0)
 
     // end of a group: the CW partial sums of every output meet in shared memory (fixed order)
-    // (the exchange buffer holds at most 4 tiles: a group of 8 is finished in two halves, JB = first tile of the half)
-    constexpr int TGF = TG > 4 ? 4 : TG;
-    auto finish_tiles = [&](int tile0, int nt_here, auto JB) {
-        constexpr int jb = decltype(JB)::value;
-        float* const mine = part + warp * (TGF * Mc * 16);   // layout part[warp][j][m][16 rows]
+    auto finish_group = [&](int tile0, int nt_here) {
+        float* const mine = part + warp * (TG * Mc * 16);   // layout part[warp][j][m][16 rows]
 #pragma unroll
-        for (int j = 0; j < TGF; ++j) {
+        for (int j = 0; j < TG; ++j) {
             if (j < nt_here) {
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     const int m = nt * 8 + 2 * q;
                     if (m < Mc) {
-                        mine[(j * Mc + m) * 16 + g] = acc[jb + j][nt][0];
-                        mine[(j * Mc + m) * 16 + g + 8] = acc[jb + j][nt][2];
+                        mine[(j * Mc + m) * 16 + g] = acc[j][nt][0];
+                        mine[(j * Mc + m) * 16 + g + 8] = acc[j][nt][2];
                     }
                     if (m + 1 < Mc) {
-                        mine[(j * Mc + m + 1) * 16 + g] = acc[jb + j][nt][1];
-                        mine[(j * Mc + m + 1) * 16 + g + 8] = acc[jb + j][nt][3];
+                        mine[(j * Mc + m + 1) * 16 + g] = acc[j][nt][1];
+                        mine[(j * Mc + m + 1) * 16 + g + 8] = acc[j][nt][3];
                     }
                 }
             }
@@ -584,8 +583,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                     const int idx = jm * 16 + 2 * pr;
 #pragma unroll
                     for (int w = 0; w < CW; ++w) {
-                        sg += part[w * (TGF * Mc * 16) + idx];
-                        su += part[w * (TGF * Mc * 16) + idx + 1];
+                        sg += part[w * (TG * Mc * 16) + idx];
+                        su += part[w * (TG * Mc * 16) + idx + 1];
                     }
                     const float gt = Elem<T>::to_f32(Elem<T>::from_f32(sg));
                     const float up = Elem<T>::to_f32(Elem<T>::from_f32(su));
@@ -595,7 +594,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
             return;
         }
-        if (p.epilogue == 2) {
+        if constexpr (GU) {
             // SwiGLU over split halves: rows 0..7 of a tile are gate_i, rows 8..15 the up_i of the same outputs
             const int pairs = nt_here * Mc * 8;
             for (int o = tid; o < pairs; o += CW * 32) {
@@ -609,8 +608,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                     const int idx = jm * 16 + pr;
 #pragma unroll
                     for (int w = 0; w < CW; ++w) {
-                        sg += part[w * (TGF * Mc * 16) + idx];
-                        su += part[w * (TGF * Mc * 16) + idx + 8];
+                        sg += part[w * (TG * Mc * 16) + idx];
+                        su += part[w * (TG * Mc * 16) + idx + 8];
                     }
                     const float gt = Elem<T>::to_f32(Elem<T>::from_f32(sg));
                     const float up = Elem<T>::to_f32(Elem<T>::from_f32(su));
@@ -630,20 +629,13 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             if (grow < r1) {
                 float sum = 0.0f;
 #pragma unroll
-                for (int w = 0; w < CW; ++w) sum += part[w * (TGF * Mc * 16) + o];
+                for (int w = 0; w < CW; ++w) sum += part[w * (TG * Mc * 16) + o];
                 if (p.bias) sum += Elem<T>::to_f32(static_cast<const T*>(p.bias)[grow]);
                 if (p.residual) sum += Elem<T>::to_f32(static_cast<const T*>(p.residual)[(int64_t)m * p.N + grow]);
                 static_cast<T*>(p.y)[(int64_t)m * p.N + grow] = Elem<T>::from_f32(sum);
             }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
-    };
-
-    auto finish_group = [&](int tile0, int nt_here) {
-        finish_tiles(tile0, min(nt_here, TGF), std::integral_constant<int, 0>());
-        if constexpr (TG > 4) {
-            if (nt_here > 4) finish_tiles(tile0 + 4, nt_here - 4, std::integral_constant<int, 4>());
-        }
     };
 
     auto zero_acc = [&]() {
@@ -698,14 +690,14 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
 
 static thread_local bool g_launch_pdl = false;   // set by the entry point for the duration of one call
 
-template <typename T, int NT, int TG, int CW, bool DQ>
-static int launch_staged_dq(const StagedParams& p, int grid, cudaStream_t stream) {
+template <typename T, int NT, int TG, int CW, bool DQ, bool GU>
+static int launch_staged_as(const StagedParams& p, int grid, cudaStream_t stream) {
     static bool configured[64] = {false};
     int dev = 0;
     NF4_CUDA_TRY(cudaGetDevice(&dev));
     NF4_REQUIRE(dev < 64, NF4_ERR_LIMIT, "gemv: device ordinal %d (at most 64 devices per process)", dev);
     if (!configured[dev]) {
-        NF4_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<T, NT, TG, CW, DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM));
+        NF4_CUDA_TRY(cudaFuncSetAttribute(gemv_staged_kernel<T, NT, TG, CW, DQ, GU>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM));
         configured[dev] = true;
     }
     if (g_launch_pdl) {
@@ -719,21 +711,24 @@ static int launch_staged_dq(const StagedParams& p, int grid, cudaStream_t stream
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_staged_kernel<T, NT, TG, CW, DQ>, p));
+        NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemv_staged_kernel<T, NT, TG, CW, DQ, GU>, p));
     } else {
-        gemv_staged_kernel<T, NT, TG, CW, DQ><<<grid, (CW + 1) * 32, GEMV_SMEM, stream>>>(p);
+        gemv_staged_kernel<T, NT, TG, CW, DQ, GU><<<grid, (CW + 1) * 32, GEMV_SMEM, stream>>>(p);
     }
     NF4_CUDA_TRY(cudaGetLastError());
     return NF4_OK;
 }
 
-// the double-quantized form exists for bf16 only (the type of every configuration that uses it)
+// the double-quantized form and the SwiGLU-over-halves epilogue exist for bf16 only (the type of every
+// configuration that uses them), and not combined
 template <typename T, int NT, int TG, int CW>
 static int launch_staged(const StagedParams& p, int grid, cudaStream_t stream) {
     if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-        if (p.absmax_u8) return launch_staged_dq<T, NT, TG, CW, true>(p, grid, stream);
+        if (p.absmax_u8 && p.epilogue != 2) return launch_staged_as<T, NT, TG, CW, true, false>(p, grid, stream);
+        if (p.epilogue == 2 && !p.absmax_u8) return launch_staged_as<T, NT, TG, CW, false, true>(p, grid, stream);
     }
-    return launch_staged_dq<T, NT, TG, CW, false>(p, grid, stream);
+    if (p.epilogue == 2) return -2;
+    return launch_staged_as<T, NT, TG, CW, false, false>(p, grid, stream);
 }
 
 // ---- tensor maps ----------------------------------------------------------------------------
@@ -846,14 +841,11 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         const int v = atoi(env);
         if (v == 8 || v == 16) CW = v;
     }
-    // (two column tiles on 8 warps whose activations come from L2: groups of 8 tiles when the CTA has that many,
-    // so the 16 x K activations are fetched half as often)
     int TG = (NT == 1 || CW == 8) ? 4 : 2;
-    if (NT == 2 && CW == 8 && tiles > 4) TG = 8;
     while (TG > 1 && TG / 2 >= tiles) TG /= 2;
     if (const char* env = getenv("NF4_GEMV_TG")) {
         const int v = atoi(env);
-        if (v == 1 || v == 2 || (v == 4 && (NT == 1 || CW == 8)) || (v == 8 && NT == 2 && CW == 8)) TG = v;
+        if (v == 1 || v == 2 || (v == 4 && (NT == 1 || CW == 8))) TG = v;
     }
 
     StagedParams p;
@@ -889,7 +881,7 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
     p.off_bars = 0;
     p.off_c256 = 256;
     p.off_part = dq ? 256 + 1024 : 256;
-    const int part_bytes = CW * (TG > 4 ? 4 : TG) * M * 16 * 4;
+    const int part_bytes = CW * TG * M * 16 * 4;
     p.off_x = (p.off_part + part_bytes + 127) & ~127;
     if (p.off_x > low_cap) return -1;
     p.x_staged = ((int64_t)p.off_x + (int64_t)M * p.x_stride <= low_cap) ? 1 : 0;
@@ -919,7 +911,6 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         if (TG == 2) NF4_SG(1, 2);
         NF4_SG(1, 1);
     } else {
-        if (TG == 8) return launch_staged<T, 2, 8, 8>(p, grid, stream);
         if (TG == 4) return launch_staged<T, 2, 4, 8>(p, grid, stream);
         if (TG == 2) NF4_SG(2, 2);
         NF4_SG(2, 1);
