@@ -600,9 +600,9 @@ def thunder_decode(cfg, batch, prompt_len, steps, warmup, dev, sampler=None):
 
 def run_prefill(args):
     """The prefill configuration (batch 8 x 2048 random token ids, causal) through the SAME jitted module: one call
-    processes the whole prompt (16384 activation rows: every linear runs on the tensor-core dequant-GEMM, attention
-    on torch's SDPA through Thunder's own executors, the glue ops eagerly -- neither nvFuser nor Inductor exists
-    here).  Timed as thunder/benchmarks/benchmark_inference.py:200-206, 467-529 times prefill: synchronise,
+    processes the whole prompt (16384 activation rows: the fused blocks run every linear on the tensor-core
+    dequant-GEMM, RMSNorm / rotary + cache write / SiLU * up as single launches of this library, and the attention
+    itself on torch's fused SDPA kernel).  Timed as thunder/benchmarks/benchmark_inference.py:200-206, 467-529 times prefill: synchronise,
     perf_counter around the call; tok/s = batch * prompt / time.  The GEMM's share of the step comes from a
     profiler pass over one more call."""
     import torch
@@ -661,7 +661,7 @@ def run_prefill(args):
         "metric": "NF4 W4A16 prefill tok/s (Llama-3-8B shape)", "value": B * T / sec, "unit": UNIT, "n_gpus": 1,
         "steps": len(times), "warmup": max(1, args.warmup), "ms_per_step": sec * 1e3, "higher_is_better": True, "dtype": "bf16",
         "data": "synthetic", "config": {"workload": f"llama3-8b-shape NF4 prefill, batch {B} x {T} tokens, causal", "parallelism": "tp1"},
-        "path": "thunder.jit(model, transforms=[NF4LinearQuant4bit, NF4DecodeFusion (declines: more than 16 rows), PrunePrologueChecks])",
+        "path": "thunder.jit(model, transforms=[NF4LinearQuant4bit, NF4DecodeFusion, PrunePrologueChecks]) on the NF4 executor: per layer RMSNorm, GEMM(q|k|v), rotary + cache write, torch SDPA over the cache, GEMM(wo), RMSNorm, GEMM(gate|up), SiLU*up, GEMM(w2)",
         "clocks": clocks, "first_call_s": first,
         "gemm": {"kernel": "gemm_tcgen05_kernel", "share_of_gpu_time": gemm_us / total_us if total_us else None,
                  "ms": gemm_us / 1e3, "TFLOPs_in_gemm_time": flops / (gemm_us * 1e-6) / 1e12 if gemm_us else None,

@@ -183,6 +183,12 @@ int nf4_b200_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int64_
  * positions[B]; q goes to q_out [B, Hq*Dh], rotated k and v go to the caches [B, Hkv, S_max, Dh]. */
 int nf4_b200_rope_append(const void* qkv, const int* positions, void* q_out, void* k_cache, void* v_cache,
                          int64_t B, int Hq, int Hkv, int Dh, int64_t S_max, float theta, void* stream);
+/* The same for a whole prompt (prefill): qkv [B, T, (Hq+2*Hkv)*Dh], positions[T] shared by the B sequences
+ * (the model's input_pos, thunder/tests/llama2_model.py:142-190 indexes its rotary tables with it); rotated q
+ * goes out in attention layout q_out [B, Hq, T, Dh], rotated k and v go to cache rows positions[t].  Dh a power of
+ * two up to 512.  A position outside [0, S_max) writes no cache row and records code 9. */
+int nf4_b200_rope_prefill(const void* qkv, const int* positions, void* q_out, void* k_cache, void* v_cache,
+                          int64_t B, int64_t T, int Hq, int Hkv, int Dh, int64_t S_max, float theta, void* stream);
 /* Single-query grouped attention over cache positions [0, positions[b]]; out [B, Hq*Dh].  Dh = 128.
  * workspace: nf4_b200_attn_decode_workspace_bytes(B, Hq, nsplit) bytes.
  * In all kernels below a positions[b] outside [0, S_max) touches no cache row: that sequence writes
@@ -268,6 +274,9 @@ int nf4_b200_tp_allreduce_emulated(const uint64_t* host_partial_ptrs, const uint
  * counterpart in the reference.
  */
 int nf4_b200_device_error(unsigned int* host_out4);
+/* Sets the status words of the current device back to "no error" (synchronises).  The words are sticky: the
+ * first error stays until this call, so that a caller who polls rarely still sees it. */
+int nf4_b200_device_error_clear(void);
 
 #ifdef __cplusplus
 }

@@ -97,6 +97,42 @@ __global__ void rope_append_kernel(const bf16* __restrict__ qkv, const int* __re
     }
 }
 
+// ---- the same for a whole prompt: qkv [B][T][(Hq + 2*Hkv) * Dh], positions[T] (shared by the sequences) -------
+// q goes out in attention layout q_out [B][Hq][T][Dh]; rotated k and v go to cache rows positions[t].  One CTA per
+// (token, sequence); 256 is a multiple of Dh/2, so a thread keeps one pair index and computes its angle once.
+__global__ void __launch_bounds__(256) rope_prefill_kernel(const bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                                           bf16* __restrict__ q_out, bf16* __restrict__ k_cache,
+                                                           bf16* __restrict__ v_cache, int T, int Hq, int Hkv, int Dh,
+                                                           int S_max, float theta) {
+    const int t = blockIdx.x, b = blockIdx.y;
+    const int pos = positions[t];
+    const bool pos_ok = position_in_range(pos, S_max);
+    const int half = Dh >> 1;
+    const int i = threadIdx.x % half;
+    const float inv_freq = powf(theta, -2.0f * (float)i / (float)Dh);
+    float sn, cs;
+    sincosf((float)pos * inv_freq, &sn, &cs);
+    const int H = Hq + 2 * Hkv;
+    const bf16* src = qkv + ((int64_t)b * T + t) * H * Dh;
+    for (int e = threadIdx.x; e < H * half; e += 256) {
+        const int head = e / half;
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + head * Dh + 2 * i));
+        if (head < Hq) {
+            *reinterpret_cast<__nv_bfloat162*>(q_out + (((int64_t)b * Hq + head) * T + t) * Dh + 2 * i) =
+                __floats2bfloat162_rn(v.x * cs - v.y * sn, v.x * sn + v.y * cs);
+        } else if (pos_ok) {
+            if (head < Hq + Hkv) {
+                *reinterpret_cast<__nv_bfloat162*>(k_cache + (((int64_t)b * Hkv + head - Hq) * S_max + pos) * Dh + 2 * i) =
+                    __floats2bfloat162_rn(v.x * cs - v.y * sn, v.x * sn + v.y * cs);
+            } else {
+                *reinterpret_cast<__nv_bfloat162*>(v_cache + (((int64_t)b * Hkv + head - Hq - Hkv) * S_max + pos) * Dh + 2 * i) =
+                    __floats2bfloat162_rn(v.x, v.y);
+            }
+        }
+    }
+    if (!pos_ok && threadIdx.x == 0) report_bad_position(b, pos);
+}
+
 // Merge of the per-split partial results of one (batch row, query head): `base` points at
 // [nsplit][Dh + 2] floats (Dh unnormalised outputs, max, sum).  One warp per head; lane s fetches
 // the (max, sum) of split s, the weights are shared by shuffle and every lane owns 4 output dims,
@@ -488,6 +524,28 @@ __global__ void silu_mul_kernel(const bf16* __restrict__ gu, bf16* __restrict__ 
     *reinterpret_cast<__nv_bfloat162*>(h + r * F + i) = __floats2bfloat162_rn(a, c);
 }
 
+// the halves layout at streaming sizes: 8 outputs per thread, 16-byte loads and stores (F % 8 == 0)
+__global__ void __launch_bounds__(256) silu_mul_halves_vec_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, int F8,
+                                                                  int64_t total8) {
+    const int64_t t = (int64_t)blockIdx.x * 256 + threadIdx.x;     // index over [rows][F/8]
+    if (t >= total8) return;
+    const int64_t r = t / F8;
+    const int c = (int)(t - r * F8);
+    const uint4 g4 = ld_nc_u128(gu + (r * 2 * F8 + c) * 8);
+    const uint4 u4 = ld_nc_u128(gu + (r * 2 * F8 + F8 + c) * 8);
+    const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 gte = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+        const float2 up = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
+        const __nv_bfloat162 y = __floats2bfloat162_rn(gte.x / (1.0f + __expf(-gte.x)) * up.x, gte.y / (1.0f + __expf(-gte.y)) * up.y);
+        ow[i] = *reinterpret_cast<const uint32_t*>(&y);
+    }
+    *reinterpret_cast<uint4*>(h + t * 8) = o;
+}
+
 __global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ y, int64_t pairs) {
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= pairs) return;
@@ -557,6 +615,11 @@ int attn_read_error(unsigned int* out4) {
     NF4_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_attn_error, sizeof(unsigned int) * 4));
     return NF4_OK;
 }
+int attn_clear_error() {
+    const unsigned int zero[4] = {0u, 0u, 0u, 0u};
+    NF4_CUDA_TRY(cudaMemcpyToSymbol(g_attn_error, zero, sizeof(zero)));
+    return NF4_OK;
+}
 
 }  // namespace nf4
 
@@ -582,6 +645,22 @@ extern "C" int nf4_b200_rope_append(const void* qkv, const int* positions, void*
     rope_append_kernel<<<grid, Dh / 2, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const bf16*>(qkv), positions, static_cast<bf16*>(q_out), static_cast<bf16*>(k_cache),
         static_cast<bf16*>(v_cache), Hq, Hkv, Dh, (int)S_max, theta);
+    NF4_CUDA_TRY(cudaGetLastError());
+    return NF4_OK;
+}
+
+extern "C" int nf4_b200_rope_prefill(const void* qkv, const int* positions, void* q_out, void* k_cache, void* v_cache,
+                                     int64_t B, int64_t T, int Hq, int Hkv, int Dh, int64_t S_max, float theta, void* stream) {
+    NF4_REQUIRE(qkv && positions && q_out && k_cache && v_cache, NF4_ERR_ARG, "rope_prefill: null pointer");
+    NF4_REQUIRE(Dh >= 2 && Dh <= 512 && 256 % (Dh / 2) == 0 && Dh % 2 == 0 && Hq > 0 && Hkv > 0, NF4_ERR_ARG,
+                "rope_prefill: head_dim %d (a power of two up to 512)", Dh);
+    NF4_REQUIRE(S_max > 0 && S_max <= 0x7fffffff && T >= 0 && T <= 0x7fffffff && B >= 0 && B <= 65535, NF4_ERR_ARG,
+                "rope_prefill: B=%lld T=%lld S_max=%lld", (long long)B, (long long)T, (long long)S_max);
+    if (B == 0 || T == 0) return NF4_OK;
+    dim3 grid((unsigned)T, (unsigned)B);
+    rope_prefill_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const bf16*>(qkv), positions, static_cast<bf16*>(q_out), static_cast<bf16*>(k_cache),
+        static_cast<bf16*>(v_cache), (int)T, Hq, Hkv, Dh, (int)S_max, theta);
     NF4_CUDA_TRY(cudaGetLastError());
     return NF4_OK;
 }
@@ -728,6 +807,14 @@ extern "C" int nf4_b200_silu_mul(const void* gate_up, void* h, int64_t rows, int
     NF4_REQUIRE(rows >= 0 && F > 0 && F % 2 == 0, NF4_ERR_ARG, "silu_mul: bad extents");
     const int64_t pairs = rows * (F / 2);
     if (pairs == 0) return NF4_OK;
+    if (!interleaved && F % 8 == 0 && rows * F >= (1 << 20) && reinterpret_cast<uintptr_t>(gate_up) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(h) % 16 == 0) {
+        const int64_t total8 = rows * (F / 8);
+        silu_mul_halves_vec_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const bf16*>(gate_up), static_cast<bf16*>(h), (int)(F / 8), total8);
+        NF4_CUDA_TRY(cudaGetLastError());
+        return NF4_OK;
+    }
     silu_mul_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const bf16*>(gate_up), static_cast<bf16*>(h), (int)F, pairs, interleaved);
     NF4_CUDA_TRY(cudaGetLastError());

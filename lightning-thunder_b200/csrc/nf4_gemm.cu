@@ -48,6 +48,11 @@ int gemm_read_error(unsigned int* out4) {
     NF4_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_gemm_error, sizeof(unsigned int) * 4));
     return NF4_OK;
 }
+int gemm_clear_error() {
+    const unsigned int zero[4] = {0u, 0u, 0u, 0u};
+    NF4_CUDA_TRY(cudaMemcpyToSymbol(g_gemm_error, zero, sizeof(zero)));
+    return NF4_OK;
+}
 
 constexpr int GM_DQ_WARPS = 16;          // dequant warps: four threads per weight row (a quarter block each)
 constexpr int GM_THREADS = (3 + GM_DQ_WARPS) * 32;   // activation producer, MMA, dequant (the first 4 also run the epilogue), weight producer

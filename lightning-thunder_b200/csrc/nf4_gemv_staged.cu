@@ -931,6 +931,9 @@ namespace nf4 {
 int gemm_read_error(unsigned int* out4);
 int attn_read_error(unsigned int* out4);
 int ar_read_error(unsigned int* out4);
+int gemm_clear_error();
+int attn_clear_error();
+int ar_clear_error();
 }
 
 extern "C" int nf4_b200_gemv_decode_fits(int64_t M, int64_t N, int64_t K, int prologue) {
@@ -963,4 +966,12 @@ extern "C" int nf4_b200_device_error(unsigned int* host_out4) {
         for (int i = 0; i < 4; ++i) host_out4[i] = g[i];
     }
     return NF4_OK;
+}
+
+extern "C" int nf4_b200_device_error_clear(void) {
+    const unsigned int zero[4] = {0u, 0u, 0u, 0u};
+    NF4_CUDA_TRY(cudaMemcpyToSymbol(g_gemv_error, zero, sizeof(zero)));
+    if (int rc = gemm_clear_error()) return rc;
+    if (int rc = attn_clear_error()) return rc;
+    return ar_clear_error();
 }

@@ -168,6 +168,11 @@ int ar_read_error(unsigned int* out4) {
     NF4_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_ar_error, sizeof(unsigned int) * 4));
     return NF4_OK;
 }
+int ar_clear_error() {
+    const unsigned int zero[4] = {0u, 0u, 0u, 0u};
+    NF4_CUDA_TRY(cudaMemcpyToSymbol(g_ar_error, zero, sizeof(zero)));
+    return NF4_OK;
+}
 
 static int ar_plan(int64_t numel, int world, int64_t buffer_bytes, ArParams* p, int* blocks_out) {
     NF4_REQUIRE(world >= 1 && world <= AR_MAX_WORLD, NF4_ERR_LIMIT, "tp_allreduce: world %d outside [1, %d]", world, AR_MAX_WORLD);

@@ -40,6 +40,7 @@ SIGNATURES = {
     "nf4_b200_linear_generic": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_ptr,
                                          _c_ptr, _c_int, _c_ptr]),
     "nf4_b200_device_error": (_c_int, [_c_ptr]),
+    "nf4_b200_device_error_clear": (_c_int, []),
     "nf4_b200_dq_quantize": (_c_int, [_c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "nf4_b200_dq_dequantize": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr]),
     "nf4_b200_linear_dq_workspace_bytes": (_c_i64, [_c_i64, _c_i64]),
@@ -53,6 +54,8 @@ SIGNATURES = {
     "nf4_b200_rmsnorm": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, ctypes.c_float, _c_ptr]),
     "nf4_b200_rope_append": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_int, _c_i64,
                                       ctypes.c_float, _c_ptr]),
+    "nf4_b200_rope_prefill": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_int, _c_int, _c_i64,
+                              ctypes.c_float, _c_ptr]),
     "nf4_b200_attn_decode_workspace_bytes": (_c_i64, [_c_i64, _c_int, _c_int]),
     "nf4_b200_attn_decode": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_int,
                                       _c_i64, _c_int, _c_ptr]),
@@ -106,6 +109,11 @@ def device_error():
     out = (ctypes.c_uint * 4)()
     check(load().nf4_b200_device_error(out), "nf4_b200_device_error")
     return tuple(out)
+
+
+def device_error_clear() -> None:
+    """Sets the (sticky) status words back to "no error"; synchronises."""
+    check(load().nf4_b200_device_error_clear(), "nf4_b200_device_error_clear")
 
 
 def check(status: int, what: str) -> None:

@@ -414,6 +414,42 @@ def attn_decode_fused(qkv: torch.Tensor, positions: torch.Tensor, k_cache: torch
     return out
 
 
+def rms_norm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """x * rsqrt(mean(x^2, -1) + eps) * weight over the last dimension of a contiguous bf16 tensor (one launch)."""
+    _require_cuda(x, "rms_norm_rows input")
+    D = x.shape[-1]
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.numel() != D or D % 2:
+        raise ValueError("rms_norm_rows: bf16 input and weight, an even last dimension")
+    x2 = x.reshape(-1, D)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    with torch.cuda.device(x.device):
+        out = torch.empty_like(x2)
+        _lib.check(_lib.load().nf4_b200_rmsnorm(x2.data_ptr(), weight.data_ptr(), out.data_ptr(), x2.shape[0], D, float(eps),
+                                                _stream_ptr(x.device)), "nf4_b200_rmsnorm")
+    return out.view(x.shape)
+
+
+def rope_prefill(qkv: torch.Tensor, positions: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, Hq: int, Hkv: int,
+                 theta: float) -> torch.Tensor:
+    """Rotary embedding of a whole prompt: qkv [B, T, (Hq+2*Hkv)*Dh] bf16, positions [T] int32.  Returns the rotated
+    queries [B, Hq, T, Dh]; the rotated keys and the values are written to cache rows positions[t] of
+    k_cache / v_cache [B, Hkv, S_max, Dh]."""
+    _require_cuda(qkv, "rope_prefill input")
+    B, T = qkv.shape[0], qkv.shape[1]
+    Dh, S_max = k_cache.shape[-1], k_cache.shape[2]
+    if (qkv.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16 or positions.dtype != torch.int32
+            or positions.numel() != T or qkv.shape[2] != (Hq + 2 * Hkv) * Dh or tuple(k_cache.shape) != (B, Hkv, S_max, Dh)
+            or v_cache.shape != k_cache.shape or not (qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous())):
+        raise ValueError("rope_prefill: bf16 qkv [B, T, (Hq+2*Hkv)*Dh], int32 positions [T], contiguous bf16 caches [B, Hkv, S, Dh]")
+    with torch.cuda.device(qkv.device):
+        q = torch.empty((B, Hq, T, Dh), dtype=qkv.dtype, device=qkv.device)
+        _lib.check(_lib.load().nf4_b200_rope_prefill(qkv.data_ptr(), positions.contiguous().data_ptr(), q.data_ptr(), k_cache.data_ptr(),
+                                                     v_cache.data_ptr(), B, T, Hq, Hkv, Dh, S_max, float(theta),
+                                                     _stream_ptr(qkv.device)), "nf4_b200_rope_prefill")
+    return q
+
+
 def silu_mul(gate_up: torch.Tensor, F: int, interleaved: bool) -> torch.Tensor:
     """[rows, 2F] -> [rows, F]: silu(gate) * up with gate/up as halves or as interleaved pairs."""
     _require_cuda(gate_up, "silu_mul input")

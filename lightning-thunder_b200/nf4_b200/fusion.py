@@ -1,4 +1,4 @@
-"""Decode-step fusions for Thunder-jitted Llama-shaped models on the NF4 executor.
+"""Block fusions for Thunder-jitted Llama-shaped models on the NF4 executor.
 
 After `NF4LinearQuant4bit` has replaced every `linear` by `nf4_b200_matmul`, a decoder layer is
 still ~70 small torch ops around 7 quantized linears.  `NF4DecodeFusion` is a second trace pass
@@ -15,8 +15,11 @@ fused kernels:
                                                                                       2 launches
     norm + linear     w(rms_norm(x))  (the output head)                               1 launch
 
-Only single-token steps (at most 16 sequences) are rewritten; a trace with more activation rows
-(prefill) keeps the generic symbols, which run on the tensor-core GEMM and the other executors.
+The same three symbols also cover traces with more activation rows (a prompt of T > 1 tokens, or more
+than 16 sequences): their implementations then run RMSNorm, the rotary embedding + cache write and
+SiLU * up as single launches of this library around the tensor-core dequant-GEMM (one GEMM over the
+q|k|v rows, one over the gate|up rows) and leave the attention itself to torch's fused SDPA kernels --
+instead of the dozens of eager element-wise launches per layer the unfused trace is executed with.
 The pass changes no parameter name, shape or value: to let Q, K and V (and gate and up) stream as
 one matrix it re-homes their packed codes and absmax into one allocation each and leaves the
 module's entries as views into it (a 64-element quantization block never crosses a row, so the
@@ -78,7 +81,7 @@ def _span(parts, what: str) -> torch.Tensor:
 
 
 def _rmsnorm_rows(x2, norm_w, eps):
-    return torch.nn.functional.rms_norm(x2, (x2.shape[-1],), norm_w, eps)
+    return functional.rms_norm_rows(x2, norm_w, eps)
 
 
 def _gemv(x2, packed, absmax, code, N, K, *, norm_w=None, eps=0.0, epilogue=0, residual=None, pdl=True, next_weight=None):
@@ -94,13 +97,50 @@ def _gemv(x2, packed, absmax, code, N, K, *, norm_w=None, eps=0.0, epilogue=0, r
                          residual=residual, pdl=pdl, next_weight=next_weight)
 
 
-def _positions_impl(input_pos, B):
-    return input_pos.to(torch.int32).expand(B).contiguous()
+def _positions_impl(input_pos, B, T):
+    """int32 positions for the kernels: one per sequence for a single-token step, one per token for a prompt."""
+    p = input_pos.to(torch.int32)
+    return p.expand(B).contiguous() if T == 1 else p.contiguous()
+
+
+def _linear(x2, packed, absmax, code, N, K):
+    return functional.linear_nf4(x2, packed, None, absmax, code, 64, (N, K))
+
+
+_mask_rows: dict = {}
+
+
+def _cache_mask(positions, S):
+    """[T, S] boolean: cache row s is visible to the token at positions[t] (s <= position)."""
+    key = (positions.device, S)
+    rows = _mask_rows.get(key)
+    if rows is None:
+        if positions.is_cuda and torch.cuda.is_current_stream_capturing():
+            rows = torch.arange(S, device=positions.device, dtype=torch.int32)
+        else:
+            rows = _mask_rows[key] = torch.arange(S, device=positions.device, dtype=torch.int32)
+    return rows[None, :] <= positions[:, None]
+
+
+def _attn_prefill(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv):
+    """The attention block over B x T rows: RMSNorm, one GEMM over the q|k|v rows, rotary embedding + cache write,
+    torch's fused attention over the cache (grouped heads, visibility from the positions), output GEMM, residual."""
+    F = functional
+    B, T, D = x.shape
+    n = F.rms_norm_rows(x.reshape(B * T, D), norm_w, eps)
+    qkv = _linear(n, _span((wq, wk, wv), "q/k/v weight"), _span((aq, ak, av), "q/k/v absmax"), code, (Hq + 2 * Hkv) * HEAD_DIM, D)
+    q4 = F.rope_prefill(qkv.view(B, T, -1), positions, k_cache, v_cache, Hq, Hkv, theta)
+    att = torch.nn.functional.scaled_dot_product_attention(q4, k_cache, v_cache, attn_mask=_cache_mask(positions, k_cache.shape[2]),
+                                                           enable_gqa=Hq != Hkv)
+    y = _linear(att.transpose(1, 2).reshape(B * T, Hq * HEAD_DIM), wo, ao, code, D, Hq * HEAD_DIM)
+    return y.view(x.shape).add_(x)
 
 
 def _attn_block_impl(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv):
     F = functional
     D = x.shape[-1]
+    if x.dim() == 3 and x.shape[1] > 1:
+        return _attn_prefill(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv)
     B = x.numel() // D
     x2 = x.reshape(B, D)
     # (the weight the next GEMV streams is hinted to each GEMV: the attention launch in between reads no weights)
@@ -117,6 +157,11 @@ def _mlp_block_impl(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim):
     B = h.numel() // D
     h2 = h.reshape(B, D)
     packed, absmax = _span((w1, w3), "gate/up weight"), _span((a1, a3), "gate/up absmax")
+    if B > MAX_ROWS:
+        # tensor-core regime: RMSNorm, one GEMM over the gate|up rows, SiLU * up, down GEMM, residual
+        gu = _linear(F.rms_norm_rows(h2, norm_w, eps), packed, absmax, code, 2 * Fdim, D)
+        y = _linear(F.silu_mul(gu, Fdim, interleaved=False), w2, a2, code, D, Fdim)
+        return y.view(h.shape).add_(h)
     if F.gemv_decode_fits(B, 2 * Fdim, D, F.PROLOGUE_RMSNORM) and F.swiglu_halves_available():
         act = _gemv(h2, packed, absmax, code, 2 * Fdim, D, norm_w=norm_w, eps=eps, epilogue=F.EPILOGUE_SWIGLU_HALVES,
                     next_weight=(w2, a2, D, Fdim))
@@ -130,7 +175,10 @@ def _mlp_block_impl(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim):
 def _norm_linear_impl(x, norm_w, eps, w, a, code, N):
     K = x.shape[-1]
     x2 = x.reshape(-1, K)
-    y = _gemv(x2, w, a, code, N, K, norm_w=norm_w, eps=eps)
+    if x2.shape[0] > MAX_ROWS:
+        y = _linear(functional.rms_norm_rows(x2, norm_w, eps), w, a, code, N, K)
+    else:
+        y = _gemv(x2, w, a, code, N, K, norm_w=norm_w, eps=eps)
     return y.view(*x.shape[:-1], N)
 
 
@@ -141,8 +189,8 @@ def get_fusion_symbols():
         return _symbols
     ex = get_nf4_executor()
 
-    def positions_meta(input_pos, B):
-        return TensorProxy(like=input_pos, shape=(B,), dtype=thunder.dtypes.int32)
+    def positions_meta(input_pos, B, T):
+        return TensorProxy(like=input_pos, shape=(B,) if T == 1 else (T,), dtype=thunder.dtypes.int32)
 
     def attn_block_meta(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv):
         return TensorProxy(like=x)
@@ -356,7 +404,7 @@ def _find_mlp(g: _Graph, i: int):
     n3, w3, a3, c3, (F3, D3) = _nf4_parts(up)
     _need(_same(n1, n3) and (F1, D1) == (Fdim, D) and (F3, D3) == (Fdim, D), "gate/up shapes")
     h, nw, eps = _match_rms_norm(g, n1, used)
-    _need(_rows(h) <= MAX_ROWS and Fdim % 8 == 0, "too many rows for the fused GEMV")
+    _need(Fdim % 8 == 0, "hidden width")
     out_b = down
     res = [j for j in g.cons.get(down.output.name, ())]
     if len(res) == 1 and g.bsyms[res[0]].sym.name == "add":
@@ -381,7 +429,8 @@ def _find_attention(g: _Graph, i: int):
     q4, k4, v4, mask, dropout, causal = args[:6]
     _need(isinstance(mask, TensorProxy) and not causal and not dropout and sdpa.kwargs.get("scale") is None, "sdpa form")
     B, Hq, T, Dh = q4.shape
-    _need(T == 1 and Dh == HEAD_DIM and B <= MAX_ROWS, "not a single-token step with 128-wide heads")
+    _need(Dh == HEAD_DIM, "heads are not 128 wide")
+    _need(T > 1 or B <= MAX_ROWS, "a single-token step of more than 16 sequences")
     S = k4.shape[2]
     # query side
     tq = g.producer(q4, "transpose", used)
@@ -451,7 +500,7 @@ def _find_attention(g: _Graph, i: int):
                 _single_use(g, o, region)
     return _Found("attn", max(region), region, add.output,
                   dict(x=x, nw=nw, eps=eps, wq=wq, aq=aq, wk=wk, ak=ak, wv=wv, av=av, wo=wo, ao=ao, code=code,
-                       k_cache=k_cache, v_cache=v_cache, pos=pos, cos=cos_t, sin=sin_t, Hq=Hq, Hkv=Hkv, B=B, S=S))
+                       k_cache=k_cache, v_cache=v_cache, pos=pos, cos=cos_t, sin=sin_t, Hq=Hq, Hkv=Hkv, B=B, T=T, S=S))
 
 
 def _find_norm_linear(g: _Graph, i: int, taken: set[int]):
@@ -459,7 +508,6 @@ def _find_norm_linear(g: _Graph, i: int, taken: set[int]):
     used = [i]
     n, w, a, code, (N, K) = _nf4_parts(lin)
     x, nw, eps = _match_rms_norm(g, n, used)
-    _need(_rows(x) <= MAX_ROWS, "too many rows")
     region = set(used)
     _need(not (region & taken), "already fused")
     _single_use(g, n, region)
@@ -471,7 +519,8 @@ def _find_norm_linear(g: _Graph, i: int, taken: set[int]):
 # ---------------------------------------------------------------------------------------------------
 
 class NF4DecodeFusion(Transform):
-    """Second pass after `NF4LinearQuant4bit` (see the module docstring).  `rope_theta` is the base of
+    """Second pass after `NF4LinearQuant4bit` (see the module docstring); it rewrites single-token traces and
+    prompt (prefill) traces alike.  `rope_theta` is the base of
     the rotary embedding the model's cos/sin tables were built with; when omitted it is read from
     `model.args.rope_theta`.  The tables found in the trace are checked against it before an attention
     block is rewritten (the fused kernel computes the angles itself)."""
@@ -616,11 +665,11 @@ class NF4DecodeFusion(Transform):
                     continue
                 if f.kind == "attn":
                     a = f.args
-                    key = (a["pos"].name, a["B"])
+                    key = (a["pos"].name, a["B"], a["T"])
                     p32 = pos32.get(key)
                     if p32 is None:
-                        p32 = TensorProxy(like=a["pos"], shape=(a["B"],), dtype=thunder.dtypes.int32)
-                        new_bsyms.append(sym["positions"].bind(a["pos"], a["B"], output=p32))
+                        p32 = TensorProxy(like=a["pos"], shape=(a["B"],) if a["T"] == 1 else (a["T"],), dtype=thunder.dtypes.int32)
+                        new_bsyms.append(sym["positions"].bind(a["pos"], a["B"], a["T"], output=p32))
                         pos32[key] = p32
                     new_bsyms.append(sym["attn_block"].bind(
                         a["x"], a["nw"], a["eps"], a["wq"], a["aq"], a["wk"], a["ak"], a["wv"], a["av"], a["wo"], a["ao"],

@@ -99,3 +99,27 @@ def cpu_attn_decode_fused(qkv, positions, k_cache, v_cache, Hq, Hkv, theta, *, p
         sc = torch.einsum("hd,hld->hl", q[b], kk) / (Dh ** 0.5)
         res[b] = torch.einsum("hl,hld->hd", torch.softmax(sc, dim=-1), vv).reshape(-1)
     return res.to(qkv.dtype)
+
+
+def cpu_rms_norm_rows(x, weight, eps):
+    xf = x.detach().float()
+    return (xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+
+
+def cpu_rope_prefill(qkv, positions, k_cache, v_cache, Hq, Hkv, theta):
+    """qkv [B, T, (Hq+2*Hkv)*Dh] -> rotated q [B, Hq, T, Dh]; rotated k and v written to cache rows positions[t]."""
+    B, T, Dh = qkv.shape[0], qkv.shape[1], k_cache.shape[-1]
+    parts = qkv.float().view(B, T, Hq + 2 * Hkv, Dh)
+    i = torch.arange(Dh // 2, dtype=torch.float32)
+    ang = positions.float().view(1, T, 1, 1) * torch.pow(torch.tensor(float(theta)), -2.0 * i / Dh).view(1, 1, 1, -1)
+    c, s = torch.cos(ang), torch.sin(ang)
+
+    def rot(t):
+        tr = t.reshape(*t.shape[:-1], Dh // 2, 2)
+        return _bf(torch.stack([tr[..., 0] * c - tr[..., 1] * s, tr[..., 0] * s + tr[..., 1] * c], dim=-1).flatten(-2))
+
+    q, k, v = rot(parts[:, :, :Hq]), rot(parts[:, :, Hq:Hq + Hkv]), parts[:, :, Hq + Hkv:]
+    idx = positions.long()
+    k_cache[:, :, idx] = k.transpose(1, 2).to(k_cache.dtype)
+    v_cache[:, :, idx] = v.transpose(1, 2).to(v_cache.dtype)
+    return q.transpose(1, 2).contiguous().to(qkv.dtype)

@@ -104,3 +104,52 @@ def test_fused_rotary_append_attention(G, nsplit, flags):
             assert torch.equal(v[b, :, p], v_ref[b, :, p])
         assert int(counters.abs().sum()) == 0
     assert _lib.device_error()[0] == 0
+
+
+def test_position_outside_the_cache_is_refused_in_the_kernel():
+    """A position outside [0, S_max) read from device memory: that sequence's cache rows stay untouched, its output
+    is zero, the other sequences are served as usual, and the status word holds code 9 with the row and the position
+    until it is cleared.  (The bounds test is a compare in the kernel: nothing faults.)"""
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    Hq, Hkv, S, theta, nsplit = 8, 2, 64, 500000.0, 3
+    g = torch.Generator(device="cuda").manual_seed(9)
+    assert _lib.device_error()[0] == 0
+    for bad in (S, -1, 1 << 20):
+        pos = torch.tensor([3, bad, 10], device="cuda", dtype=torch.int32)
+        B = 3
+        k = torch.randn((B, Hkv, S, DH), device="cuda", generator=g).to(torch.bfloat16)
+        v = torch.randn((B, Hkv, S, DH), device="cuda", generator=g).to(torch.bfloat16)
+        k0, v0 = k.clone(), v.clone()
+        ws = torch.empty((lib.nf4_b200_attn_decode_workspace_bytes(B, Hq, nsplit),), device="cuda", dtype=torch.uint8)
+        counters = torch.zeros((B * Hkv,), device="cuda", dtype=torch.int32)
+        out = torch.full((B, Hq * DH), 7.0, device="cuda", dtype=torch.bfloat16)
+        qkv = torch.randn((B, (Hq + 2 * Hkv) * DH), device="cuda", generator=g).to(torch.bfloat16)
+        _lib.check(lib.nf4_b200_attn_decode_fused(qkv.data_ptr(), pos.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                                  ws.data_ptr(), counters.data_ptr(), B, Hq, Hkv, DH, S, nsplit, theta, 0, st),
+                   "attn_decode_fused")
+        torch.cuda.synchronize()
+        assert torch.equal(k[1], k0[1]) and torch.equal(v[1], v0[1])       # nothing written for the refused row
+        assert not out[1].any()                                            # ... and it attends to nothing
+        assert not torch.equal(k[0], k0[0]) and out[0].any() and out[2].any()
+        code, row, where, count = _lib.device_error()
+        assert code == 9 and row == 1 and where == (bad & 0xffffffff) and count >= 1
+        # the prompt form: the same refusal per token
+        q4 = functional_rope_prefill(qkv.view(1, B, -1).contiguous(), pos, torch.zeros_like(k[:1]), torch.zeros_like(v[:1]), Hq, Hkv, theta)
+        assert q4.shape == (1, Hq, B, DH)
+        _lib.device_error_clear()
+        assert _lib.device_error() == (0, 0, 0, 0)
+
+
+def functional_rope_prefill(qkv, pos, kc, vc, Hq, Hkv, theta):
+    from nf4_b200 import _lib, functional
+
+    k0, v0 = kc.clone(), vc.clone()
+    q4 = functional.rope_prefill(qkv, pos, kc, vc, Hq, Hkv, theta)
+    torch.cuda.synchronize()
+    changed = (kc != k0).any(dim=-1).any(dim=1)[0].nonzero().flatten().tolist()     # cache rows that were written
+    assert sorted(changed) == sorted(int(p) for p in pos.tolist() if 0 <= int(p) < kc.shape[2])
+    assert _lib.device_error()[0] == 9
+    return q4

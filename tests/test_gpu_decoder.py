@@ -201,6 +201,16 @@ def test_glue_kernels_against_torch():
     torch.testing.assert_close(h.float(), _bf(torch.nn.functional.silu(gf[:, :1024]) * gf[:, 1024:]), rtol=1e-2, atol=1e-2)
     _lib.check(lib.nf4_b200_silu_mul(gu.data_ptr(), h.data_ptr(), 3, 1024, 1, st), "silu_mul")
     torch.testing.assert_close(h.float(), _bf(torch.nn.functional.silu(gf[:, 0::2]) * gf[:, 1::2]), rtol=1e-2, atol=1e-2)
+    # prompt-sized input (the 16-byte form of the halves layout): bit-identical to the small-size kernel row by row
+    gu = torch.randn((300, 2 * 3584), device="cuda", generator=g).to(torch.bfloat16)
+    h = torch.empty((300, 3584), device="cuda", dtype=torch.bfloat16)
+    _lib.check(lib.nf4_b200_silu_mul(gu.data_ptr(), h.data_ptr(), 300, 3584, 0, st), "silu_mul")
+    h_rows = torch.empty_like(h)
+    for r0 in range(0, 300, 100):       # 100 x 3584 < 2^20 outputs: the element-pair kernel
+        _lib.check(lib.nf4_b200_silu_mul(gu[r0:r0 + 100].data_ptr(), h_rows[r0:r0 + 100].data_ptr(), 100, 3584, 0, st), "silu_mul")
+    assert torch.equal(h, h_rows)
+    gf = gu.float()
+    torch.testing.assert_close(h.float(), _bf(torch.nn.functional.silu(gf[:, :3584]) * gf[:, 3584:]), rtol=1e-2, atol=1e-2)
     logits = torch.randn((4, 128256), device="cuda", generator=g).to(torch.bfloat16)
     ids = torch.empty((4,), device="cuda", dtype=torch.int64)
     _lib.check(lib.nf4_b200_argmax(logits.data_ptr(), ids.data_ptr(), 4, 128256, st), "argmax")

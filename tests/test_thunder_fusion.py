@@ -8,7 +8,7 @@ GPU tests run them on the kernels and compare with the oracle-backed unfused mod
 import pytest
 import torch
 
-from helpers import cpu_attn_decode_fused, cpu_gemv_decode, cpu_silu_mul
+from helpers import cpu_attn_decode_fused, cpu_gemv_decode, cpu_rms_norm_rows, cpu_rope_prefill, cpu_silu_mul
 from test_thunder_integration import _oracle_linear_nf4, _oracle_quantize_4bit
 
 thunder_support = pytest.importorskip("nf4_b200.thunder_support")
@@ -31,6 +31,8 @@ def cpu_backend(monkeypatch):
     monkeypatch.setattr(functional, "gemv_decode_fits", lambda M, N, K, prologue: True)
     monkeypatch.setattr(functional, "attn_decode_fused", cpu_attn_decode_fused)
     monkeypatch.setattr(functional, "silu_mul", cpu_silu_mul)
+    monkeypatch.setattr(functional, "rms_norm_rows", cpu_rms_norm_rows)
+    monkeypatch.setattr(functional, "rope_prefill", cpu_rope_prefill)
     monkeypatch.setattr(functional, "swiglu_halves_available", lambda: True)
     monkeypatch.setattr(NF4LinearQuant4bit, "quantize_weight", lambda self, w: functional.quantize_4bit(w, quant_type="nf4"))
 
@@ -118,24 +120,44 @@ def test_parameters_keep_names_shapes_and_values_cpu(cpu_backend):
         assert torch.equal(jf.state_dict()[k], v), k
 
 
-def test_prefill_trace_is_left_alone_cpu(cpu_backend):
-    """More than 16 activation rows: the pass declines (those linears belong to the tensor-core GEMM) and
-    says why for the attention."""
+def test_prefill_trace_is_rewritten_too_cpu(cpu_backend):
+    """A prompt of 24 tokens (more than the fused GEMV's 16 rows): the same block symbols, whose implementations run
+    on the GEMM and the one-launch glue kernels; logits and KV cache match the unfused jitted module, and decoding
+    continues from that cache on the single-token blocks."""
     args = tiny_args(max_batch=1)
     fusion = NF4DecodeFusion()
-    jf = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), fusion], executors=(get_nf4_executor(),))
+    ex = get_nf4_executor()
+    jf = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), fusion], executors=(ex,))
+    ju = thunder.jit(build(args), transforms=[NF4LinearQuant4bit()], executors=(ex,))
     tok = torch.randint(0, args.vocab_size, (1, 24))
-    y = jf(tok, torch.arange(24))
+    y, yu = jf(tok, torch.arange(24)), ju(tok, torch.arange(24))
     assert y.shape == (1, 1, args.vocab_size)
     names = _names(thunder.last_traces(jf)[-1])
-    assert "nf4_b200_attn_block" not in names and "nf4_b200_mlp_block" not in names
-    assert names.count("nf4_b200_matmul") == 7 * args.n_layers       # the head's single row is still fused
-    assert names.count("nf4_b200_norm_linear") == 1
-    assert fusion.declined and "single-token" in fusion.declined[0]
+    assert names.count("nf4_b200_attn_block") == args.n_layers and names.count("nf4_b200_mlp_block") == args.n_layers
+    assert "nf4_b200_matmul" not in names and names.count("nf4_b200_norm_linear") == 1 and not fusion.declined
+    torch.testing.assert_close(y.float(), yu.float(), rtol=3e-2, atol=3e-2)
+    for name, buf in jf._model.named_buffers():
+        if name.endswith("k_cache") or name.endswith("v_cache"):
+            other = dict(ju._model.named_buffers())[name]
+            torch.testing.assert_close(buf[:, :, :24].float(), other[:, :, :24].float(), rtol=3e-2, atol=3e-2)
+            assert not buf[:, :, 24:].any()
     # the same module then decodes token by token on the fused blocks (a second trace for the new shapes)
-    y1 = jf(torch.randint(0, args.vocab_size, (1, 1)), torch.tensor([24]))
-    assert y1.shape == (1, 1, args.vocab_size)
+    nxt = torch.randint(0, args.vocab_size, (1, 1))
+    y1, y1u = jf(nxt, torch.tensor([24])), ju(nxt, torch.tensor([24]))
     assert "nf4_b200_attn_block" in _names(thunder.last_traces(jf)[-1])
+    torch.testing.assert_close(y1.float(), y1u.float(), rtol=3e-2, atol=3e-2)
+
+
+def test_many_sequences_single_token_attention_is_declined_cpu(cpu_backend):
+    """A single-token step of more than 16 sequences: the attention kernel's limit; the MLP blocks still fuse."""
+    args = tiny_args(max_batch=20, n_layers=1)
+    fusion = NF4DecodeFusion()
+    jf = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), fusion], executors=(get_nf4_executor(),))
+    y = jf(torch.randint(0, args.vocab_size, (20, 1)), torch.tensor([0]))
+    assert y.shape == (20, 1, args.vocab_size)
+    names = _names(thunder.last_traces(jf)[-1])
+    assert "nf4_b200_attn_block" not in names and names.count("nf4_b200_mlp_block") == 1
+    assert fusion.declined and "16 sequences" in fusion.declined[0]
 
 
 def test_other_rope_base_is_declined_cpu(cpu_backend):
@@ -200,3 +222,70 @@ def test_greedy_step_claims_embedding_and_argmax_gpu():
     region = [b for b in thunder.last_traces(js)[-1].bound_symbols if "CUDAGraph" in b.sym.name][0]
     inner = [s.sym.name for s in region.subsymbols]
     assert "nf4_b200_embedding" in inner and "nf4_b200_argmax" in inner
+
+
+@pytest.mark.gpu
+def test_fused_prefill_on_kernels_matches_oracle_backend(monkeypatch):
+    """A 40-token prompt for 2 sequences through the fused blocks on the GPU (RMSNorm, rotary + cache write and
+    SiLU * up as single launches, the linears on the dequant-GEMM, torch's fused attention over the cache), then
+    three single-token steps from that cache -- against the unfused module on the CPU oracle."""
+    from nf4_b200 import _lib
+
+    B, T = 2, 40
+    args = tiny_args(dim=512, n_heads=4, n_kv_heads=2, hidden_dim=1024, vocab_size=2048, max_seq_len=64, max_batch=B)
+    ex = get_nf4_executor()
+    fusion = NF4DecodeFusion()
+    jg = thunder.jit(build(args, "cuda"), transforms=[NF4LinearQuant4bit(), fusion], executors=(ex,))
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, args.vocab_size, (B, T), generator=g)
+    steps = [torch.randint(0, args.vocab_size, (B, 1), generator=g) for _ in range(3)]
+
+    def run(jm, dev):
+        outs = [jm(prompt.to(dev), torch.arange(T, device=dev)).float().cpu()]
+        for i, tok in enumerate(steps):
+            outs.append(jm(tok.to(dev), torch.tensor([T + i], device=dev)).float().cpu())
+        return torch.stack(outs)
+
+    got = run(jg, "cuda")
+    assert fusion.fused["attn"] == 2 * args.n_layers and fusion.fused["mlp"] == 2 * args.n_layers and not fusion.declined
+    assert _lib.device_error()[0] == 0
+    caches = {n: b.float().cpu() for n, b in jg._model.named_buffers() if n.endswith("_cache")}
+    monkeypatch.setattr(functional, "quantize_4bit", _oracle_quantize_4bit)
+    monkeypatch.setattr(functional, "linear_nf4", _oracle_linear_nf4)
+    monkeypatch.setattr(NF4LinearQuant4bit, "quantize_weight", lambda self, w: functional.quantize_4bit(w, quant_type="nf4"))
+    jc = thunder.jit(build(args, "cpu"), transforms=[NF4LinearQuant4bit()], executors=(ex,))
+    want = run(jc, "cpu")
+    torch.testing.assert_close(got, want, rtol=5e-2, atol=5e-2)
+    assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.9
+    for n, b in jc._model.named_buffers():
+        if n.endswith("_cache"):
+            torch.testing.assert_close(caches[n], b.float(), rtol=5e-2, atol=5e-2)
+            assert not caches[n][:, :, T + 3:].any()
+
+
+@pytest.mark.gpu
+def test_rope_prefill_kernel_matches_the_single_token_kernel():
+    """The prompt form of the rotary embedding writes the same cache rows (bit for bit) as feeding the tokens one
+    by one through nf4_b200_rope_append, and returns the same rotated queries in attention layout."""
+    import ctypes
+
+    from nf4_b200 import _lib
+
+    lib = _lib.load()
+    B, T, Hq, Hkv, Dh, S = 3, 37, 8, 2, 128, 48
+    g = torch.Generator(device="cuda").manual_seed(4)
+    qkv = torch.randn((B, T, (Hq + 2 * Hkv) * Dh), device="cuda", generator=g).to(torch.bfloat16)
+    pos = torch.randperm(S, device="cuda", generator=g)[:T].to(torch.int32)
+    kc, vc = (torch.zeros((B, Hkv, S, Dh), device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    q4 = functional.rope_prefill(qkv, pos, kc, vc, Hq, Hkv, 5e5)
+    kr, vr = torch.zeros_like(kc), torch.zeros_like(vc)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for t in range(T):
+        q1 = torch.empty((B, Hq * Dh), device="cuda", dtype=torch.bfloat16)
+        row = qkv[:, t].contiguous()
+        p = pos[t].expand(B).contiguous()
+        _lib.check(lib.nf4_b200_rope_append(row.data_ptr(), p.data_ptr(), q1.data_ptr(), kr.data_ptr(), vr.data_ptr(), B, Hq, Hkv, Dh,
+                                            S, 5e5, st), "rope_append")
+        assert torch.equal(q4[:, :, t], q1.view(B, Hq, Dh))
+    assert torch.equal(kc, kr) and torch.equal(vc, vr)
+    assert _lib.device_error()[0] == 0
