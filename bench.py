@@ -37,6 +37,25 @@ for _p in (ROOT, os.path.join(ROOT, "lightning-thunder_b200")):
 
 UNIT = "tok/s"
 
+_result_out = None
+
+
+def _claim_stdout() -> None:
+    """The contract is ONE JSON line on stdout.  Libraries write there too (NCCL prints its version banner to
+    stdout when NCCL_DEBUG is set in the environment), so file descriptor 1 is pointed at stderr for the rest of
+    the process and the result line goes to a saved copy of the original stdout."""
+    global _result_out
+    if _result_out is None:
+        sys.stdout.flush()
+        _result_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(obj) -> None:
+    out = _result_out if _result_out is not None else sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
+
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -172,7 +191,7 @@ def run_reference(args):
         # no whole step runs on the CPU: ms_per_step is one layer's linears scaled to the model
         "extrapolated": True,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # --------------------------------------------------------------------------------------------
@@ -263,7 +282,7 @@ def run_kernel(args):
     if args.kernel == "gemm":
         tf = 2.0 * M * N * K / us / 1e6
         out.update({"TFLOPs": tf, "tensor_frac_of_" + src: tf / peaks["bf16_tflops"]})
-    print(json.dumps(out))
+    emit(out)
 
 
 def run_attention(args):
@@ -317,7 +336,7 @@ def run_attention(args):
     us = statistics.median(ts)
     alg = B * Hkv * (ctx + 1) * Dh * 2 * 2
     peaks, src = measured_peaks()
-    print(json.dumps({"kernel": "attention", "B": B, "Hq": Hq, "Hkv": Hkv, "ctx": ctx, "splits": ns, "us_per_launch": us,
+    emit(({"kernel": "attention", "B": B, "Hq": Hq, "Hkv": Hkv, "ctx": ctx, "splits": ns, "us_per_launch": us,
                       "algorithmic_bytes": alg, "GBps": alg / us / 1e3, "hbm_frac_of_" + src: alg / us / 1e3 / peaks["hbm_gbs"],
                       "buffers": L, "device_error": list(_lib.device_error())}))
 
@@ -657,7 +676,7 @@ def run_prefill(args):
                               + 3 * cfg.ffn * cfg.d_model)
     flops = 2.0 * B * T * weights
     peaks, src = measured_peaks()
-    print(json.dumps({
+    emit(({
         "metric": "NF4 W4A16 prefill tok/s (Llama-3-8B shape)", "value": B * T / sec, "unit": UNIT, "n_gpus": 1,
         "steps": len(times), "warmup": max(1, args.warmup), "ms_per_step": sec * 1e3, "higher_is_better": True, "dtype": "bf16",
         "data": "synthetic", "config": {"workload": f"llama3-8b-shape NF4 prefill, batch {B} x {T} tokens, causal", "parallelism": "tp1"},
@@ -830,7 +849,7 @@ def run_decode(args):
     if "nccl_exchange_tok_s" in eng:
         line["exchange"] = {"kind": eng["exchange"], "tok_s": eng["tok_s"], "nccl_all_reduce_tok_s": eng["nccl_exchange_tok_s"],
                             "nccl_all_reduce_ms_per_step": eng["nccl_exchange_ms_per_step"]}
-    print(json.dumps(line))
+    emit(line)
     finish()
 
 
@@ -856,6 +875,7 @@ def main():
     ap.add_argument("--nbuf", type=int, default=None)
     ap.add_argument("--dq", action="store_true", help="--kernel gemv/gemm: double-quantized absmax (8-bit, blocks of 256)")
     args = ap.parse_args()
+    _claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     elif args.kernel == "attention":

@@ -13,6 +13,7 @@ def test_reference_arm_json_line():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
                          capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert out.returncode == 0, out.stderr[-2000:]
+    assert len(out.stdout.strip().splitlines()) == 1, "stdout must hold the JSON line and nothing else"
     line = json.loads(out.stdout.strip().splitlines()[-1])
     for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
                 "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
@@ -29,3 +30,14 @@ def test_reference_arm_json_line():
     assert set(line["config"]) == set(want)
     for k in ("workload", "parallelism", "global_batch", "context", "blocksize", "double_quant"):
         assert line["config"][k] == want[k], k
+
+
+def test_only_the_result_line_reaches_stdout():
+    """Whatever else writes to file descriptor 1 after start-up (NCCL prints its version banner there when NCCL_DEBUG
+    is set) lands on stderr: bench.py keeps a private copy of stdout for its one JSON line."""
+    code = ("import os, sys; sys.argv=['bench.py']; sys.path.insert(0, %r); import bench; bench._claim_stdout(); "
+            "os.write(1, b'library banner\\n'); print('python-level chatter'); bench.emit({'ok': 1})" % ROOT)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout == '{"ok": 1}\n'
+    assert "library banner" in out.stderr and "python-level chatter" in out.stderr
