@@ -856,7 +856,7 @@ def run_decode(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128, help="timed steps (decode: tokens generated; the workload's 128 new tokens by default)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None, "llama3-8b", "llama3-70b", "tiny", "llama3-8b-prefill"])

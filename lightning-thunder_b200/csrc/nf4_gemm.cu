@@ -25,6 +25,18 @@
 // Split K (few weight tiles): CTAs of one tile park fp32 partial sums in a workspace, bump an arrival
 // counter, and the last one adds the partials in range order (deterministic) and runs the epilogue.
 //
+// PAIR (template flag; 256-row tiles, no K split, an even number of weight tiles): two CTAs of a cluster -- two
+// adjacent weight tiles, the same 256 activation rows -- run as one `cta_group::2` MMA of 256 weight rows.  Each
+// CTA dequantises its own 128 rows into its own tensor memory and loads only HALF of the activation tile (128 rows,
+// 16 KB per K block instead of 32 KB) into its shared memory; the leader (cluster rank 0) issues every MMA, which
+// reads the activation halves from both CTAs.  Per CTA that halves the L2 -> shared-memory traffic (16 instead of
+// 32 KB per K block) and doubles the ring to six stages.  MEASURED 3-10 % SLOWER than one CTA per tile (the period
+// of a K-block group is set by dequantise -> hand-off -> multiply -> hand-off, and every hand-off now crosses the
+// pair), so it is off unless NF4_GEMM_PAIR=1.  Hand-offs across the pair: the peer's activation loads
+// complete on the LEADER's `full` barrier (cp.async.bulk.tensor with .cta_group::2, no multicast), the peer's
+// dequant warps arrive on the leader's `a_ready`, and the leader's tcgen05.commit arrives on `done` / `acc_done`
+// of both CTAs (.multicast::cluster).
+//
 // Every mbarrier wait is bounded; a time-out sets a status word (nf4_b200_device_error code 5..9),
 // the CTA stops waiting and runs to its end (TMEM is always released).
 #include <cuda.h>
@@ -61,7 +73,10 @@ constexpr int GM_BM = 128;               // weight rows per CTA (UMMA M)
 constexpr int GM_MAX_STAGES = 8;         // activation stages: 8 (tiles up to 64 rows), 4 (128 rows) or 3 (256 rows)
 constexpr int GM_DONE = 8;               // ring of "MMAs up to here have completed" barriers, one per release unit
 constexpr int GM_A_COLS = 32;            // TMEM columns of one K block of weights: 64 bf16 per row, two per column
-constexpr int GM_GROUPS = 2;             // weight groups (GM_WKB K blocks each) in TMEM: one converts while one multiplies
+constexpr int GM_GKB = 4;                // K blocks per weight group in TMEM (a whole packed stage)
+constexpr int GM_GROUPS = 2;             // weight groups in TMEM: one converts while one multiplies.  Four groups of 2 blocks (a hand-off
+                                         // after every 2 blocks, more slack between the two sides) measured 7 % SLOWER: the extra
+                                         // tcgen05.wait::st + arrival per packed stage costs the dequant warps more than the slack gives
 constexpr int GM_A_COL0 = 256;           // accumulator in TMEM columns [0, 256), weight groups in [256, 512)
 constexpr int GM_TMEM_COLS = 512;
 constexpr int GM_MAX_WSTAGES = 4;        // packed-weight stages, each GM_WKB K blocks deep: 4, or 3 for 256-row tiles
@@ -180,6 +195,46 @@ __device__ __forceinline__ void gm_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// ---- two-CTA (cta_group::2) forms -------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t gm_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t gm_mapa(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void gm_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void gm_mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load into this CTA's shared memory whose bytes complete on a barrier that may live in the pair's other CTA
+__device__ __forceinline__ void gm_tma_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[tmem of both CTAs] . B[smem halves of both CTAs]^T, 256 x N x 16
+__device__ __forceinline__ void gm_mma_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t z = 0u;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.u32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
+}
+// the barrier at this shared-memory offset in BOTH CTAs gets one arrival once every MMA issued so far has completed
+__device__ __forceinline__ void gm_commit_pair(uint32_t bar) {
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+
 // 32 lanes x 16 columns of fp32 from tensor memory into 16 registers per thread
 __device__ __forceinline__ void gm_tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
@@ -202,36 +257,48 @@ __device__ __forceinline__ uint64_t gm_smem_desc(uint32_t addr) {
 }
 
 // Instruction descriptor: D = f32, A = B = bf16, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t gm_instr_desc(int n) {
+__device__ __forceinline__ uint32_t gm_instr_desc(int n, int m = GM_BM) {
     uint32_t d = 0;
     d |= 1u << 4;                      // D format f32
     d |= 1u << 7;                      // A format bf16
     d |= 1u << 10;                     // B format bf16
     d |= (uint32_t)(n >> 3) << 17;     // N >> 3
-    d |= (uint32_t)(GM_BM >> 4) << 24; // M >> 4
+    d |= (uint32_t)(m >> 4) << 24;     // M >> 4 (256 for a CTA pair: 128 rows in each CTA)
     return d;
 }
 
+template <bool PAIR>
 __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int TM = p.TM;
-    const int b_bytes = TM * 128;
+    const uint32_t cta_rank = PAIR ? gm_cluster_rank() : 0u;     // 0: the CTA that issues the pair's MMAs
+    const int TML = PAIR ? TM >> 1 : TM;                          // activation rows this CTA loads per K block
+    const int b_bytes = TML * 128;
     const int NS = p.stages, NW = p.wstages;
 
     // The host laid the buffers out in shared-window addresses around the table's window [64K, 128K),
     // assuming the dynamic region starts at or below GM_LOW_BASE.
-    const uint32_t s0 = gm_smem_u32(smem);
+    // Shared-memory addresses.  The host laid the buffers out as offsets into the CTA's shared window.  Outside a
+    // cluster (and in rank 0 of one) the window starts at address 0 and an offset IS the address.  In rank 1 of a
+    // cluster the window starts higher (the address of a shared variable carries the CTA's rank above the offset
+    // bits; a window is smaller than 2^18 bytes) and a bare offset is not an address of this CTA at all -- a plain
+    // ld.shared with it traps.  So every address below is rebased by W, this CTA's window base; `to_leader`
+    // turns an address of this CTA into the leader's (for barriers the pair shares).
+    const uint32_t base_full = gm_smem_u32(smem);
+    const uint32_t s0 = base_full & 0x3ffffu;          // offset of the dynamic region inside the window
+    const uint32_t W = PAIR ? base_full - s0 : 0u;
+    const uint32_t to_leader = PAIR ? gm_mapa(base_full, 0u) - base_full : 0u;
     if (s0 > GM_LOW_BASE) {
         if (tid == 0 && atomicCAS(&g_gemm_error[0], 0u, 10u) == 0u) g_gemm_error[1] = s0;
         return;
     }
-    const uint32_t full0 = p.bar_addr, done0 = full0 + 8 * GM_MAX_STAGES, aready0 = done0 + 8 * GM_DONE,
+    const uint32_t full0 = p.bar_addr + W, done0 = full0 + 8 * GM_MAX_STAGES, aready0 = done0 + 8 * GM_DONE,
                    accdone = aready0 + 8 * GM_GROUPS, wfull0 = accdone + 8,
                    wempty0 = wfull0 + 8 * GM_MAX_WSTAGES, flags0 = wempty0 + 8 * GM_MAX_WSTAGES;
     const uint32_t desc0 = flags0 + 16;              // activation descriptors per stage (8 x 8 bytes)
     const int ru_shift = p.ru_shift, ru_mask = (1 << ru_shift) - 1;
-    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + (flags0 - s0));
+    uint32_t* const tmem_slot = reinterpret_cast<uint32_t*>(smem + (flags0 - W - s0));
     volatile int* const abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* const last_flag = abort_flag + 1;
 
@@ -248,7 +315,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) gm_mbar_init(full0 + 8 * s, 1);
         for (int s = 0; s < GM_DONE; ++s) gm_mbar_init(done0 + 8 * s, 1);   // tcgen05.commit after a unit's MMAs
-        for (int g = 0; g < GM_GROUPS; ++g) gm_mbar_init(aready0 + 8 * g, GM_DQ_WARPS);   // one arrival per dequant warp
+        for (int g = 0; g < GM_GROUPS; ++g) gm_mbar_init(aready0 + 8 * g, (PAIR ? 2 : 1) * GM_DQ_WARPS);   // one arrival per dequant warp (of both CTAs)
         for (int s = 0; s < NW; ++s) {
             gm_mbar_init(wfull0 + 8 * s, 1);
             gm_mbar_init(wempty0 + 8 * s, GM_DQ_WARPS);   // every dequant warp has read its rows
@@ -262,7 +329,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        // TMEM allocation by one full warp; the base address lands in shared memory
+        // TMEM allocation by one full warp; the base address lands in shared memory.  In a pair each CTA
+        // allocates its own tensor memory (all 512 columns of an empty TMEM: the same base in both CTAs)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(flags0), "r"(GM_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -272,11 +340,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         const float mine = __bfloat162float(__float2bfloat16_rn(__ldg(p.code16 + (lane & 15))));
         for (int e = warp - 2; e < 256; e += GM_DQ_WARPS) {
             const float first = __shfl_sync(0xffffffffu, mine, e >> 4), second = __shfl_sync(0xffffffffu, mine, e & 15);
-            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(GM_LUT_WINDOW + (uint32_t)(e * 256 + lane * 8)), "f"(first), "f"(second) : "memory");
+            asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(W + GM_LUT_WINDOW + (uint32_t)(e * 256 + lane * 8)), "f"(first), "f"(second) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) gm_cluster_sync();      // the other CTA's barriers exist before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_slot;
     if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -293,8 +362,14 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
             }
             if (lane == 0) {
                 const uint32_t fb = full0 + 8 * slot;
-                gm_mbar_expect_tx(fb, (uint32_t)b_bytes);
-                gm_tma_2d(p.b_addr[slot], &p.xmap, kb * 64, m0, fb);
+                if (PAIR) {
+                    // both halves of the stage complete on the leader's barrier, which the leader arms for both
+                    if (cta_rank == 0) gm_mbar_expect_tx(fb, 2u * (uint32_t)b_bytes);
+                    gm_tma_2d_pair(W + p.b_addr[slot], &p.xmap, kb * 64, m0 + (int)cta_rank * TML, fb + to_leader);
+                } else {
+                    gm_mbar_expect_tx(fb, (uint32_t)b_bytes);
+                    gm_tma_2d(W + p.b_addr[slot], &p.xmap, kb * 64, m0, fb);
+                }
             }
             __syncwarp();
             if (++slot == NS) slot = 0;
@@ -310,28 +385,29 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
             gm_wait(wempty0 + 8 * wslot, wparity ^ 1u, abort_flag, 9, kb);
             if (lane == 0) {
                 gm_mbar_expect_tx(wfull0 + 8 * wslot, (uint32_t)(GM_PK_BYTES + (p.am_tma ? GM_AM_BYTES : 0)));
-                gm_tma_2d(p.w_addr[wslot], &p.wmap, kb * 32, n0, wfull0 + 8 * wslot);
-                if (p.am_tma) gm_tma_2d(p.am_addr[wslot], &p.amap, kb, n0, wfull0 + 8 * wslot);
+                gm_tma_2d(W + p.w_addr[wslot], &p.wmap, kb * 32, n0, wfull0 + 8 * wslot);
+                if (p.am_tma) gm_tma_2d(W + p.am_addr[wslot], &p.amap, kb, n0, wfull0 + 8 * wslot);
             }
             __syncwarp();
             if (++wslot == NW) { wslot = 0; wparity ^= 1u; }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 && cta_rank == 0) {
         // ------------------------------------ MMA issuer ---------------------------------------
-        // per group of GM_WKB K blocks: one wait for the dequantised weights, 4 MMAs per K block as its
+        // (PAIR: only the leader's; its MMAs run on both CTAs' tensor cores)
+        // per group of GM_GKB K blocks: one wait for the dequantised weights, 4 MMAs per K block as its
         // activations land, one commit per K block (frees the activation stage) and one per group.
         // This warp's instruction stream is serial and sits on the critical path of small tiles, so the
         // descriptors are built once and the loop body is kept short.
-        const uint32_t idesc = gm_instr_desc(TM);
+        const uint32_t idesc = PAIR ? gm_instr_desc(TM, 2 * GM_BM) : gm_instr_desc(TM);
         int slot = 0, g = 0, i = 0;              // i: K block index inside this CTA's range
         uint32_t parity = 0, gparity = 0;
         uint32_t accumulate = 0u;
         const int nkb = kb_end - kb_begin;
-        for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GM_WKB) {
+        for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GM_GKB) {
             gm_wait(aready0 + 8 * g, gparity, abort_flag, 7, kb0);     // the group's weights are in TMEM
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int nblk = min(GM_WKB, kb_end - kb0);
-            uint32_t a_tmem = tmem_d + (uint32_t)(GM_A_COL0 + g * GM_WKB * GM_A_COLS);
+            const int nblk = min(GM_GKB, kb_end - kb0);
+            uint32_t a_tmem = tmem_d + (uint32_t)(GM_A_COL0 + g * GM_GKB * GM_A_COLS);
             for (int j = 0; j < nblk; ++j, a_tmem += GM_A_COLS, ++i) {
                 gm_wait(full0 + 8 * slot, parity, abort_flag, 5, kb0 + j);  // activations landed
                 if (lane == 0) {
@@ -339,20 +415,32 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
                     asm volatile("ld.shared.b64 %0, [%1];" : "=l"(bdesc) : "r"(desc0 + 8 * slot));
                     // 16 K elements per instruction: 8 TMEM columns of the weights, 32 bytes (+2 in the
                     // descriptor's address field) inside the activations' swizzle atom
-                    gm_mma(tmem_d, a_tmem, bdesc, idesc, accumulate);
-                    gm_mma(tmem_d, a_tmem + 8u, bdesc + 2u, idesc, 1u);
-                    gm_mma(tmem_d, a_tmem + 16u, bdesc + 4u, idesc, 1u);
-                    gm_mma(tmem_d, a_tmem + 24u, bdesc + 6u, idesc, 1u);
+                    if (PAIR) {
+                        gm_mma_pair(tmem_d, a_tmem, bdesc, idesc, accumulate);
+                        gm_mma_pair(tmem_d, a_tmem + 8u, bdesc + 2u, idesc, 1u);
+                        gm_mma_pair(tmem_d, a_tmem + 16u, bdesc + 4u, idesc, 1u);
+                        gm_mma_pair(tmem_d, a_tmem + 24u, bdesc + 6u, idesc, 1u);
+                    } else {
+                        gm_mma(tmem_d, a_tmem, bdesc, idesc, accumulate);
+                        gm_mma(tmem_d, a_tmem + 8u, bdesc + 2u, idesc, 1u);
+                        gm_mma(tmem_d, a_tmem + 16u, bdesc + 4u, idesc, 1u);
+                        gm_mma(tmem_d, a_tmem + 24u, bdesc + 6u, idesc, 1u);
+                    }
                     // one commit per release unit (and at the end of the range)
-                    if (((i + 1) & ru_mask) == 0 || i == nkb - 1) gm_commit(done0 + 8 * ((i >> ru_shift) & (GM_DONE - 1)));
+                    if (((i + 1) & ru_mask) == 0 || i == nkb - 1) {
+                        const uint32_t db = done0 + 8 * ((i >> ru_shift) & (GM_DONE - 1));
+                        if (PAIR) gm_commit_pair(db); else gm_commit(db);
+                    }
                 }
                 accumulate = 1u;
                 if (++slot == NS) { slot = 0; parity ^= 1u; }
             }
             if (++g == GM_GROUPS) { g = 0; gparity ^= 1u; }
         }
-        if (lane == 0) gm_commit(accdone);
+        if (lane == 0) { if (PAIR) gm_commit_pair(accdone); else gm_commit(accdone); }
         __syncwarp();
+    } else if (warp == 1) {
+        // the other CTA's MMA warp has nothing to issue; it releases tensor memory at the end
     } else {
         // ------------------------------------ dequant warps -------------------------------------
         // a warp may touch only the TMEM lane quarter warp % 4, so rows follow that numbering
@@ -360,7 +448,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
         const int r = q * 32 + lane;            // weight row inside the tile = TMEM lane
         const int part = (warp - 2) >> 2;       // which quarter of the row's 64-block: packed bytes [8*part, 8*part+8)
         const int grow = n0 + r;
-        const uint32_t window_lane = GM_LUT_WINDOW | (uint32_t)(lane << 3);
+        const uint32_t window_lane = (W + GM_LUT_WINDOW) | (uint32_t)(lane << 3);
         const float* const am_row = p.absmax + (int64_t)(grow < p.N ? grow : 0) * p.KB;
         const bool row_ok = grow < p.N;
         // this thread's 8 bytes of K block j of a packed stage: 16-byte chunk 2j + part/2 at its swizzled place
@@ -382,52 +470,61 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
                     am_nxt[j] = (row_ok && kb0 + GM_WKB + j < kb_end) ? __ldg(am_row + kb0 + GM_WKB + j) : 0.0f;
                 }
             }
-            const int gi = (kb0 - kb_begin) / GM_WKB;
             gm_wait(wfull0 + 8 * wslot, wparity, abort_flag, 5, kb0);   // packed bytes (and absmax) landed
             if (p.am_tma)
                 asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(am[0]), "=f"(am[1]), "=f"(am[2]), "=f"(am[3])
-                             : "r"(p.am_addr[wslot] + (uint32_t)(r * 16)));
+                             : "r"(W + p.am_addr[wslot] + (uint32_t)(r * 16)));
             uint2 w[GM_WKB];
 #pragma unroll
             for (int j = 0; j < GM_WKB; ++j)
                 asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w[j].x), "=r"(w[j].y)
-                             : "r"(p.w_addr[wslot] + pk_off + (uint32_t)(((2 * j + chunk0) ^ rsw) << 4)));
-            if (gi >= GM_GROUPS) {   // these TMEM columns held group gi-2: its last K block's unit must be done
-                const int u = ((gi - GM_GROUPS) * GM_WKB + GM_WKB - 1) >> ru_shift;
-                gm_wait(done0 + 8 * (u % GM_DONE), (uint32_t)((u / GM_DONE) & 1), abort_flag, 6, kb0);
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                             : "r"(W + p.w_addr[wslot] + pk_off + (uint32_t)(((2 * j + chunk0) ^ rsw) << 4)));
+            // the packed stage feeds GM_WKB / GM_GKB groups; each is handed to the tensor core as soon as it is in TMEM
 #pragma unroll
-            for (int j = 0; j < GM_WKB; ++j) {
-                // 8 packed bytes -> 16 weights: all 8 lookups in flight, then scale and round.  Blocks past the
-                // end of the range convert whatever the box brought; no MMA reads them.
-                float f[16];
-                gm_lookup<0>(w[j].x, window_lane, f[0], f[1]);
-                gm_lookup<1>(w[j].x, window_lane, f[2], f[3]);
-                gm_lookup<2>(w[j].x, window_lane, f[4], f[5]);
-                gm_lookup<3>(w[j].x, window_lane, f[6], f[7]);
-                gm_lookup<0>(w[j].y, window_lane, f[8], f[9]);
-                gm_lookup<1>(w[j].y, window_lane, f[10], f[11]);
-                gm_lookup<2>(w[j].y, window_lane, f[12], f[13]);
-                gm_lookup<3>(w[j].y, window_lane, f[14], f[15]);
-                uint32_t out[8];
+            for (int h = 0; h < GM_WKB / GM_GKB; ++h) {
+                if (kb0 + h * GM_GKB >= kb_end) break;          // the range ends inside this packed stage
+                const int gi = (kb0 - kb_begin) / GM_GKB + h;
+                if (gi >= GM_GROUPS) {   // these TMEM columns held group gi - GM_GROUPS: its last K block's unit must be done
+                    const int u = ((gi - GM_GROUPS) * GM_GKB + GM_GKB - 1) >> ru_shift;
+                    gm_wait(done0 + 8 * (u % GM_DONE), (uint32_t)((u / GM_DONE) & 1), abort_flag, 6, kb0);
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int i = 0; i < 8; ++i) out[i] = gm_scale_pack(f[2 * i], f[2 * i + 1], am[j]);
-                // 8 columns (16 consecutive K elements) of this thread's lane
-                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                                 ::"r"(tcol + (uint32_t)((g * GM_WKB + j) * GM_A_COLS)), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]),
-                                   "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+                for (int jj = 0; jj < GM_GKB; ++jj) {
+                    const int j = h * GM_GKB + jj;
+                    // 8 packed bytes -> 16 weights: all 8 lookups in flight, then scale and round.  Blocks past the
+                    // end of the range convert whatever the box brought; no MMA reads them.
+                    float f[16];
+                    gm_lookup<0>(w[j].x, window_lane, f[0], f[1]);
+                    gm_lookup<1>(w[j].x, window_lane, f[2], f[3]);
+                    gm_lookup<2>(w[j].x, window_lane, f[4], f[5]);
+                    gm_lookup<3>(w[j].x, window_lane, f[6], f[7]);
+                    gm_lookup<0>(w[j].y, window_lane, f[8], f[9]);
+                    gm_lookup<1>(w[j].y, window_lane, f[10], f[11]);
+                    gm_lookup<2>(w[j].y, window_lane, f[12], f[13]);
+                    gm_lookup<3>(w[j].y, window_lane, f[14], f[15]);
+                    uint32_t out[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) out[i] = gm_scale_pack(f[2 * i], f[2 * i + 1], am[j]);
+                    // 8 columns (16 consecutive K elements) of this thread's lane
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                                     ::"r"(tcol + (uint32_t)((g * GM_GKB + jj) * GM_A_COLS)), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]),
+                                       "r"(out[4]), "r"(out[5]), "r"(out[6]), "r"(out[7]) : "memory");
+                }
+                // the group is in TMEM: hand it over
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR) gm_mbar_arrive_cluster(aready0 + 8 * g + to_leader);    // the leader waits for both CTAs' weights
+                    else gm_mbar_arrive(aready0 + 8 * g);
+                }
+                if (++g == GM_GROUPS) { g = 0; gparity ^= 1u; }
             }
-            // the packed stage has been consumed, the group is in TMEM: one hand-off each per 4 K blocks
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            // the packed stage has been consumed
             __syncwarp();
-            if (lane == 0) {
-                gm_mbar_arrive(wempty0 + 8 * wslot);
-                gm_mbar_arrive(aready0 + 8 * g);
-            }
+            if (lane == 0) gm_mbar_arrive(wempty0 + 8 * wslot);
             if (++wslot == NW) { wslot = 0; wparity ^= 1u; }
-            if (++g == GM_GROUPS) { g = 0; gparity ^= 1u; }
         }
         if (warp >= 6) goto done;               // the epilogue needs one warp per TMEM lane quarter
         // ------------------------------------ epilogue ------------------------------------------
@@ -444,14 +541,15 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
             // every MMA has completed), then store rows of y 16 bytes per lane.  Stage s holds rows
             // [s * TM/2, (s+1) * TM/2) of the tile, 256 bytes (128 columns of y) each.
             const float bias = (p.bias && gn < p.N) ? __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[gn]) : 0.0f;
-            const int half = TM >> 1;
+            const int rps_shift = PAIR ? 6 : (TM == 256 ? 7 : TM == 128 ? 6 : TM == 64 ? 5 : 4);   // rows of y per stage buffer: stage bytes / 256
+            const int rps_mask = (1 << rps_shift) - 1;
             for (int c0 = 0; c0 < mlim; c0 += 16) {
                 uint32_t v[16];
                 gm_tmem_ld16(tacc + (uint32_t)c0, v);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int m = c0 + j;
-                    const uint32_t dst = p.b_addr[m >= half ? 1 : 0] + (uint32_t)((m >= half ? m - half : m) * 256 + r * 2);
+                    const uint32_t dst = W + p.b_addr[m >> rps_shift] + (uint32_t)((m & rps_mask) * 256 + r * 2);
                     const __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(v[j]) + bias);
                     asm volatile("st.shared.b16 [%0], %1;" ::"r"(dst), "h"(*reinterpret_cast<const unsigned short*>(&h)) : "memory");
                 }
@@ -461,7 +559,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
             const int chunk = et & 15;                    // 16-byte chunk of a 256-byte row
             const bool col_ok = n0 + chunk * 8 < p.N;
             for (int m = et >> 4; m < mlim; m += 8) {
-                const uint32_t src = p.b_addr[m >= half ? 1 : 0] + (uint32_t)((m >= half ? m - half : m) * 256 + chunk * 16);
+                const uint32_t src = W + p.b_addr[m >> rps_shift] + (uint32_t)((m & rps_mask) * 256 + chunk * 16);
                 uint4 d;
                 asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(d.x), "=r"(d.y), "=r"(d.z), "=r"(d.w) : "r"(src));
                 if (col_ok) *reinterpret_cast<uint4*>(y + (int64_t)(m0 + m) * p.N + n0 + chunk * 8) = d;
@@ -541,6 +639,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tcgen05_kernel(const __gri
     }
 done:
     __syncthreads();
+    if (PAIR) gm_cluster_sync();      // neither CTA leaves (or frees tensor memory) while the other may still touch it
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(GM_TMEM_COLS) : "memory");
@@ -570,7 +669,7 @@ static GmEncodeFn gm_encode_fn() {
 // Shared-memory map in shared-window addresses: the lookup table owns [64K, 128K); activation stages, packed
 // stages and the barriers are dealt, 1024-byte aligned, first into [GM_LOW_BASE, 64K), then from 128K up.
 // Returns the dynamic shared memory to request (the region starts at or below GM_LOW_BASE).
-static int gemm_layout(int TM, GemmParams* p) {
+static int gemm_layout(int TM, bool pair, GemmParams* p) {
     uint32_t low = GM_LOW_BASE, high = 2 * GM_LUT_WINDOW;
     auto place = [&](uint32_t bytes) {
         const uint32_t size = (bytes + 1023u) & ~1023u;
@@ -581,11 +680,13 @@ static int gemm_layout(int TM, GemmParams* p) {
     };
     // activation ring and release unit: 8 stages freed 4 at a time for small tiles, 4 freed in pairs for
     // 128-row tiles, 3 freed one by one for 256-row tiles (all that fits beside the table)
-    const int stages = TM > 128 ? 3 : TM > 64 ? 4 : 8, ru = TM > 128 ? 1 : TM > 64 ? 2 : 4;
+    // (a CTA of a pair holds half of the activation tile per stage: six stages of 16 KB in the same space)
+    int stages = TM > 128 ? 3 : TM > 64 ? 4 : 8, ru = TM > 128 ? 1 : TM > 64 ? 2 : 4;
+    if (pair) { stages = 6; ru = 1; }
     const int wstages = TM > 128 ? 3 : GM_MAX_WSTAGES;
     if (p) { p->stages = stages; p->wstages = wstages; p->ru_shift = ru == 4 ? 2 : ru == 2 ? 1 : 0; }
     for (int s = 0; s < stages; ++s) {
-        const uint32_t a = place((uint32_t)TM * 128u);
+        const uint32_t a = place((uint32_t)(pair ? TM / 2 : TM) * 128u);
         if (p) p->b_addr[s] = a;
     }
     for (int s = 0; s < wstages; ++s) {
@@ -676,7 +777,13 @@ static int gemm_tcgen05(const void* x, int64_t M, int64_t K, const uint8_t* pack
         splits = 1;
     p.TM = TM;
     p.splits = splits;
-    const int smem_bytes = gemm_layout(TM, &p);
+    // two CTAs per tile pair (see the head of this file): tall tiles, no K split, weight tiles in pairs.  Correct
+    // but measured 3-10 % slower than one CTA per tile on every shape tried, so it runs only when asked for
+    bool pair = false;
+    if (const char* e = getenv("NF4_GEMM_PAIR")) {
+        pair = atoi(e) == 1 && TM == 256 && splits == 1 && ntiles % 2 == 0 && ex.epilogue == 0;
+    }
+    const int smem_bytes = gemm_layout(TM, pair, &p);
     p.absmax = absmax; p.code16 = code16; p.bias = bias; p.y = y;
     p.residual = ex.residual; p.epilogue = ex.epilogue; p.pdl = ex.pdl;
     p.counters = static_cast<unsigned*>(ex.workspace);
@@ -707,7 +814,7 @@ static int gemm_tcgen05(const void* x, int64_t M, int64_t K, const uint8_t* pack
     {
         const cuuint64_t dim[2] = {(cuuint64_t)K, (cuuint64_t)M};
         const cuuint64_t str[1] = {(cuuint64_t)K * 2};
-        const cuuint32_t box[2] = {64, (cuuint32_t)TM};
+        const cuuint32_t box[2] = {64, (cuuint32_t)(pair ? TM / 2 : TM)};
         CUresult r = enc(&p.xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dim, str, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -717,7 +824,8 @@ static int gemm_tcgen05(const void* x, int64_t M, int64_t K, const uint8_t* pack
     int dev = 0;
     NF4_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 64 && !configured[dev]) {
-        NF4_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        NF4_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        NF4_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
         configured[dev] = true;
     }
     dim3 grid((unsigned)ntiles, (unsigned)(mtiles * splits));
@@ -727,12 +835,24 @@ static int gemm_tcgen05(const void* x, int64_t M, int64_t K, const uint8_t* pack
     cfg.blockDim = dim3(GM_THREADS);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (ex.pdl) {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
+    if (pair) {
+        attr[nattr].id = cudaLaunchAttributeClusterDimension;
+        attr[nattr].val.clusterDim.x = 2;
+        attr[nattr].val.clusterDim.y = 1;
+        attr[nattr].val.clusterDim.z = 1;
+        ++nattr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = ex.pdl ? 1 : 0;
-    NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel, p));
+    cfg.numAttrs = nattr;
+    if (pair) NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<true>, p));
+    else NF4_CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<false>, p));
     return NF4_OK;
 }
 

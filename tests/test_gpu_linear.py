@@ -163,6 +163,29 @@ def test_gemm_shapes(nf4_code_np, M, N, K):
     assert _lib.device_error()[0] == 0
 
 
+@pytest.mark.parametrize("N,K,M", [(512, 256, 512), (256, 512, 300), (1024, 1024, 1000), (2304, 4096, 257)])
+def test_gemm_cta_pair_matches_single_cta(N, K, M, monkeypatch):
+    """The two-CTA form of the GEMM (NF4_GEMM_PAIR=1: a cluster of two weight tiles as one cta_group::2 MMA, each CTA
+    loading half of the activation tile) computes the same sums in the same order as the single-CTA kernel: identical
+    bits, ragged M included, and no status word."""
+    import nf4_b200
+    from nf4_b200 import _lib
+
+    g = torch.Generator(device="cuda").manual_seed(N + M)
+    w = (torch.randn((N, K), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    x = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
+    packed, qs = nf4_b200.quantize_4bit(w)
+    monkeypatch.setenv("NF4_GEMM_PAIR", "0")
+    y_single = nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs).clone()
+    monkeypatch.setenv("NF4_GEMM_PAIR", "1")
+    y_pair = nf4_b200.matmul_4bit(x, packed.t(), quant_state=qs)
+    torch.cuda.synchronize()
+    assert _lib.device_error()[0] == 0
+    assert torch.equal(y_pair, y_single)
+    ref = x.float() @ nf4_b200.dequantize_4bit(packed, qs).float().t()
+    torch.testing.assert_close(y_pair.float(), ref, rtol=RTOL, atol=2 * ATOL)
+
+
 def test_gemm_full_prefill_tile_properties(nf4_code_np):
     """Config-4-sized problem (2048 activation rows, 14336x4096): compared with an fp32 matmul on the
     GEMM's own weight definition (torch is only the checker), plus linearity."""
