@@ -303,6 +303,11 @@ def linear_nf4_dq(x: torch.Tensor, packed: torch.Tensor, bias, state: QuantState
             workspace = _dq_workspace(x.device, int(lib.nf4_b200_linear_dq_workspace_bytes(N, K)))
         if out is None:
             out = torch.empty((*x.shape[:-1], N), dtype=x.dtype, device=x.device)
+        if not fused and M > 16 and x.dtype == torch.bfloat16 and workspace.numel() >= 4 * (N * K // 64) and workspace.data_ptr() % 16 == 0:
+            # tensor-core regime: expand once (this library's kernel), then the regular linear, which also plans
+            # the split-K workspace the C entry point has no argument for
+            absmax = expand_absmax(state, out=workspace[: 4 * (N * K // 64)].view(torch.float32))
+            return linear_nf4(x, packed, bias, absmax, state.code, 64, (N, K), out=out)
         _lib.check(
             lib.nf4_b200_linear_dq(x2.data_ptr(), M, K, packed.data_ptr(), state.absmax.data_ptr(),
                                    state.state2.absmax.data_ptr(), state.offset.data_ptr(), state.state2.code.data_ptr(),
