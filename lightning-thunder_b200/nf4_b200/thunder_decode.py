@@ -23,6 +23,8 @@ from torch import nn
 from .fusion import NF4DecodeFusion
 from .thunder_executor import NF4LinearQuant4bit, get_nf4_executor, thunder
 
+from thunder.core.transform_common import Transform  # noqa: E402
+
 
 def _graph_transform():
     """thunder.transforms.cudagraph.CUDAGraphTransform with a cheaper per-call path for modules with hundreds
@@ -51,12 +53,31 @@ def _graph_transform():
             graph.replay()
             return static_outputs
 
-    class Transform(CUDAGraphTransform):
+    class _Transform(CUDAGraphTransform):
         def __init__(self, *, share_mem_pool: bool = False):
             super().__init__(share_mem_pool=share_mem_pool)
             self.cuda_graph_runner = Runner(share_mem_pool=share_mem_pool)
 
-    return Transform()
+    return _Transform()
+
+
+class PinModuleMembers(Transform):
+    """Registers every parameter and buffer that the earlier transforms left alone as an override of itself
+    (`ThunderModule._overrides_parameters` / `_overrides_buffers`, the mechanism of thunder/core/module.py:58-72).
+    The prologue fetches each member on every call; an override is a dictionary hit, anything else goes through
+    torch's `get_parameter` / `get_buffer`, which walk the dotted path module by module -- about 130 such walks
+    per decode step for a 32-layer model (norm weights, KV caches, rotary tables).  Values are the same tensor
+    objects, so in-place updates (the KV cache, `load_state_dict`) stay visible; place it after the transforms
+    that replace members."""
+
+    def transform_module(self, model) -> None:
+        inner = model._model
+        for name, p in inner.named_parameters(remove_duplicate=False):
+            if p.device.type != "meta":
+                model._overrides_parameters.setdefault(name, p)
+        for name, b in inner.named_buffers(remove_duplicate=False):
+            if b.device.type != "meta":
+                model._overrides_buffers.setdefault(name, b)
 
 
 class GreedyStep(nn.Module):
@@ -88,6 +109,7 @@ def compile_decoder(model: nn.Module, *, fuse: bool = True, cuda_graph: bool = T
         transforms.append(fusion)
     transforms += list(extra_transforms)
     if prune_checks:
+        transforms.append(PinModuleMembers())
         transforms.append(PrunePrologueChecks())
     if cuda_graph:
         transforms.append(_graph_transform())

@@ -160,6 +160,29 @@ def test_many_sequences_single_token_attention_is_declined_cpu(cpu_backend):
     assert fusion.declined and "16 sequences" in fusion.declined[0]
 
 
+def test_pinned_members_are_the_same_objects_cpu(cpu_backend):
+    """PinModuleMembers: every parameter and buffer the other transforms left alone becomes an override of itself
+    (the same tensor object, so in-place updates stay visible), quantized members keep their overrides, the state
+    dict is unchanged and the module decodes the same logits."""
+    from nf4_b200.thunder_decode import PinModuleMembers
+
+    args = tiny_args()
+    ex = get_nf4_executor()
+    plain = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), NF4DecodeFusion()], executors=(ex,))
+    pinned = thunder.jit(build(args), transforms=[NF4LinearQuant4bit(), NF4DecodeFusion(), PinModuleMembers()], executors=(ex,))
+    inner = pinned._model
+    for name, p in inner.named_parameters(remove_duplicate=False):
+        assert name in pinned._overrides_parameters
+        if not name.endswith(("wq.weight", "wk.weight", "wv.weight", "wo.weight", "w1.weight", "w2.weight", "w3.weight", "output.weight")):
+            assert pinned._overrides_parameters[name] is p, name
+    for name, b in inner.named_buffers(remove_duplicate=False):
+        assert pinned._overrides_buffers[name] is b, name
+    assert pinned.get_parameter("layers.0.attention.wq.weight").dtype == torch.uint8      # the quantized override won
+    for k, v in plain.state_dict().items():
+        assert torch.equal(pinned.state_dict()[k], v), k
+    torch.testing.assert_close(_decode(pinned, 3, 2, args.vocab_size), _decode(plain, 3, 2, args.vocab_size), rtol=0, atol=0)
+
+
 def test_other_rope_base_is_declined_cpu(cpu_backend):
     args = tiny_args()
     fusion = NF4DecodeFusion(rope_theta=10000.0)          # the module's tables use 500000
