@@ -8,6 +8,8 @@ Transform stack, in order:
   NF4LinearQuant4bit      every nn.Linear -> NF4 weights + the `nf4_b200_matmul` symbol   (the drop-in for
                           thunder.transforms.quantization.BitsAndBytesLinearQuant4bit)
   NF4DecodeFusion         single-token traces: attention / MLP blocks -> fused kernels     (nf4_b200.fusion)
+  PinModuleMembers        untouched parameters / buffers become overrides of themselves: the prologue's per-call
+                          fetch of every member is a dictionary hit
   PrunePrologueChecks     drops the per-call re-validation of module members               (thunder/transforms/
                           prune_prologue_checks.py, what thunder/recipes/base.py:103-112 installs)
   CUDAGraphTransform      the computation replays as one CUDA graph                        (thunder/transforms/
