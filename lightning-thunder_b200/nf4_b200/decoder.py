@@ -230,12 +230,9 @@ class NF4Decoder:
             self._ev_end(ev, w, B)
             self._n += 1
             return
-        if swiglu and not lib.nf4_b200_gemv_decode_fits(B, w.N, w.K, prologue):
-            self._linear_decode(x, w, self.gu, prologue=prologue, norm_w=norm_w, stream=stream)
-            ck(lib.nf4_b200_silu_mul(self.gu.data_ptr(), y.data_ptr(), B, w.N // 2, 1, stream), "silu_mul")
-            self._n += 1
-            return
         if prologue and not lib.nf4_b200_gemv_decode_fits(B, w.N, w.K, prologue):
+            # the activations do not fit beside the kernel's tables (more than 8 rows of a wide model): the prologue
+            # runs as its own launch; the epilogue does not depend on that and stays fused
             if prologue == 1:
                 ck(lib.nf4_b200_rmsnorm(x.data_ptr(), norm_w.data_ptr(), self.xn.data_ptr(), B, w.K, cfg.norm_eps, stream), "rmsnorm")
                 x = self.xn
@@ -244,6 +241,11 @@ class NF4Decoder:
                 x = self.h
             self._n += 1
             prologue, norm_w = 0, None
+        if swiglu and not lib.nf4_b200_gemv_decode_fits(B, w.N, w.K, prologue):
+            self._linear_decode(x, w, self.gu, prologue=prologue, norm_w=norm_w, stream=stream)
+            ck(lib.nf4_b200_silu_mul(self.gu.data_ptr(), y.data_ptr(), B, w.N // 2, 1, stream), "silu_mul")
+            self._n += 1
+            return
         if next_w is not None and self.prefetch_next:
             ck(lib.nf4_b200_gemv_decode_next_weight(next_w.packed.data_ptr(), next_w.absmax.data_ptr(), next_w.N, next_w.K),
                "nf4_b200_gemv_decode_next_weight")

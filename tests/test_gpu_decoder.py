@@ -144,6 +144,37 @@ def test_batched_decode_on_tensor_cores(use_graph):
     assert _lib.device_error()[0] == 0
 
 
+def test_sixteen_sequences_wide_model_on_the_gemv():
+    """16 sequences of a model 1024 wide: the activations no longer fit beside the GEMV's tables, so RMSNorm runs as
+    its own launch while the SwiGLU and residual epilogues stay fused (the shape of the tensor-parallel 70B step)."""
+    from nf4_b200 import _lib
+    from nf4_b200.decoder import NF4Decoder, tiny_config
+
+    cfg = tiny_config(n_layers=2, d_model=1024, n_heads=8, n_kv_heads=2, ffn=2048, vocab=2048)
+    B = 16
+    dec = NF4Decoder(cfg, batch=B, max_seq=16, device="cuda:0", seed=6)
+    assert not dec.tensor_core and not dec.lib.nf4_b200_gemv_decode_fits(B, 2 * cfg.ffn, cfg.d_model, 1)
+    assert dec.lib.nf4_b200_gemv_decode_fits(B, 2 * cfg.ffn, cfg.d_model, 0)
+    dec.capture()
+    # per layer: norm, qkv, attention, o, norm, gate|up (SwiGLU inside), down; + embed, final norm, head, argmax
+    assert dec.launches_per_step == 7 * cfg.n_layers + 4
+    ref = TorchRef(dec)
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(0, cfg.vocab, (B, 4), generator=g).cuda()
+    dec.reset()
+    agree = 0
+    for t in range(toks.shape[1]):
+        pos = dec.positions.clone().long()
+        dec.ids_in.copy_(toks[:, t])
+        dec.run_step()
+        torch.cuda.synchronize()
+        want = ref.step(toks[:, t], pos)
+        torch.testing.assert_close(dec.logits.float(), want, rtol=3e-2, atol=3e-2)
+        agree += int((dec.ids_out == want.argmax(-1)).sum())
+    assert agree >= B * toks.shape[1] - 3
+    assert _lib.device_error()[0] == 0
+
+
 def test_fused_and_unfused_steps_agree_bitwise():
     """Prologue fusion, the one-launch attention and programmatic dependent launch change the
     schedule, not the arithmetic: same tokens and same logits as the kernel-per-op chain."""
