@@ -70,7 +70,6 @@ struct alignas(64) StagedParams {
     // offsets from the start of dynamic shared memory
     int off_bars, off_part, off_x;
     int off_c256;    // DQ: the 256-entry table of the second quantization (1 KB)
-    int AU;          // DQ: row pitch of the uint8 absmax box inside a stage (SB + 16); it sits behind the fp32 rows
     int h_base, h_rem;   // halves of 8 rows per CTA: h_base, plus one for the first h_rem CTAs
     // L2 prefetch of the next launch's weights (null: none): same row split, applied to its N
     const uint8_t* pf_packed;
@@ -167,8 +166,10 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
 // One stage of one warp: BPW 64-blocks of a 16-row tile.  Per block: 16 table lookups, 4 chained
 // MMAs per column tile (the chains of different blocks interleave), one scaling by the block's
 // absmax.  HALF: rows 8..15 of the tile do not exist (their fragment registers stay zero).
-// The BPW blocks of a warp are adjacent, so their fp32 absmax values come with one load per row (with double
-// quantization the producer warp has expanded the stage's uint8 indices into the same fp32 rows beforehand).
+// The BPW blocks of a warp are adjacent, so their absmax values (or, with double quantization, their uint8
+// indices) come with one load per row.  DQ: sc[0/1] are the second-level scales of this lane's two rows -- a
+// stage never straddles a group of 256 first-level blocks -- fetched by the caller before it waited for the
+// stage; c256 is the shared-memory table, dq_off the offset.
 template <int BPW>
 __device__ __forceinline__ void load_absmax(uint32_t addr, float (&am)[BPW]) {
     if constexpr (BPW == 2) {
@@ -177,10 +178,20 @@ __device__ __forceinline__ void load_absmax(uint32_t addr, float (&am)[BPW]) {
         asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(am[0]), "=f"(am[1]), "=f"(am[2]), "=f"(am[3]) : "r"(addr));
     }
 }
-template <typename T, int NT, int BPW, bool HALF>
+template <int BPW>
+__device__ __forceinline__ void load_absmax_dq(uint32_t addr, uint32_t c256, float scale, float dq_off, float (&am)[BPW]) {
+    uint32_t bytes;
+    if constexpr (BPW == 2) asm volatile("ld.shared.u16 %0, [%1];" : "=r"(bytes) : "r"(addr));
+    else asm volatile("ld.shared.u32 %0, [%1];" : "=r"(bytes) : "r"(addr));
+#pragma unroll
+    for (int bi = 0; bi < BPW; ++bi) am[bi] = fmaf(lds32f(c256 + 4u * ((bytes >> (8 * bi)) & 0xffu)), scale, dq_off);
+}
+
+template <typename T, int NT, int BPW, bool HALF, bool DQ>
 __device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a_off)[BPW], uint32_t am_off,
                                               uint32_t rs8, uint32_t as8, uint32_t window_lane,
-                                              const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4]) {
+                                              const uint32_t (&xf)[BPW][NT][8], float (&acc)[NT][4],
+                                              const float (&sc)[2], uint32_t c256, float dq_off) {
     uint2 wa[BPW], wb[BPW];
     float ama[BPW], amb[BPW];
 #pragma unroll
@@ -188,8 +199,13 @@ __device__ __forceinline__ void stage_compute(uint32_t sbase, const uint32_t (&a
         wa[bi] = lds64(sbase + a_off[bi]);
         if (!HALF) wb[bi] = lds64(sbase + a_off[bi] + rs8);
     }
-    load_absmax<BPW>(sbase + am_off, ama);
-    if (!HALF) load_absmax<BPW>(sbase + am_off + as8, amb);
+    if (DQ) {
+        load_absmax_dq<BPW>(sbase + am_off, c256, sc[0], dq_off, ama);
+        if (!HALF) load_absmax_dq<BPW>(sbase + am_off + as8, c256, sc[1], dq_off, amb);
+    } else {
+        load_absmax<BPW>(sbase + am_off, ama);
+        if (!HALF) load_absmax<BPW>(sbase + am_off + as8, amb);
+    }
     float tmp[BPW][NT][4];
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
@@ -257,7 +273,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     float* const part = reinterpret_cast<float*>(smem + p.off_part);
     const uint32_t xs_u32 = s0 + (uint32_t)p.off_x;
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + SG_MAX_STAGES * 8, xbar = full0 + 2 * SG_MAX_STAGES * 8;
-    const uint32_t ready0 = full0 + (2 * SG_MAX_STAGES + 2) * 8;      // DQ: the stage's absmax has been expanded to fp32
 
     // rows are dealt out in halves of 8: a CTA owns [8*h0, 8*h1); full 16-row tiles first, then at
     // most one half tile
@@ -295,7 +310,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
             for (int s = 0; s < p.NS; ++s) {
                 mbar_init(full0 + s * 8, 1);
                 mbar_init(empty0 + s * 8, CW);
-                if (DQ) mbar_init(ready0 + s * 8, 1);
             }
             *abort_flag = 0;
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -303,84 +317,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"n"((CW + 1) * 32) : "memory");
         griddep_launch();
-        if constexpr (DQ) {
-            // Double-quantized absmax: besides issuing the boxes this warp turns each stage's uint8 indices into fp32
-            // (absmax = fma(code256[u8], scale2[block / 256], offset)) in the rows the compute warps read, a few
-            // stages behind its own issuing, so the compute warps run the same instruction stream as without double
-            // quantization.  Lane l expands row l / 2, half l % 2 of the stage's SB blocks; a stage never straddles
-            // a group of 256 first-level blocks (SB divides K / 64 and 256), so one scale serves a row of a stage.
-            float* const c256 = reinterpret_cast<float*>(smem + p.off_c256);
-            for (int i = lane; i < 256; i += 32) c256[i] = __ldg(p.code256 + i);
-            const float dq_off = __ldg(p.offset);
-            __syncwarp();
-            const uint32_t c256_u32 = s0 + (uint32_t)p.off_c256;
-            // stages between issuing and expanding: NS - 2, so that the stage after the one the compute warps work on
-            // is already expanded when they hand theirs back (the wait for a free slot below comes first in an iteration)
-            const int lag = p.NS > 2 ? p.NS - 2 : 1;
-            const int er = lane >> 1, eh = lane & 1, enb = p.SB >> 1;       // row, half, blocks per lane (8 or 16)
-            struct Cursor { int tile0, nt, seg, j; bool half; };
-            auto start = [&](Cursor& c) { c.tile0 = 0; c.seg = 0; c.j = 0; c.half = 0 >= nfull; c.nt = c.half ? 1 : min(TG, nfull); };
-            auto advance = [&](Cursor& c) {
-                if (++c.j == c.nt) {
-                    c.j = 0;
-                    if (++c.seg == p.nseg) {
-                        c.seg = 0;
-                        c.tile0 += c.nt;
-                        c.half = c.tile0 >= nfull;
-                        c.nt = c.half ? 1 : min(TG, nfull - c.tile0);
-                    }
-                }
-            };
-            Cursor ci, ce;
-            start(ci);
-            start(ce);
-            int issued = 0, expanded = 0;
-            auto expand = [&]() {
-                const int slot_e = expanded % p.NS;
-                const uint32_t par_e = (uint32_t)((expanded / p.NS) & 1);
-                mbar_wait(full0 + slot_e * 8, par_e, abort_flag, 1, expanded);
-                const int row0 = r0 + (ce.tile0 + ce.j) * 16;
-                if (!(ce.half && er >= 8)) {
-                    const int row = min(row0 + er, p.N - 1);
-                    const float sc = __ldg(p.scale2 + (((int64_t)row * p.KB + ce.seg * p.SB) >> 8));
-                    const uint32_t sbase = ring_u32 + (uint32_t)slot_e * (uint32_t)p.stage_bytes;
-                    const uint32_t src = sbase + 16u * (uint32_t)(p.RS + p.AS) + (uint32_t)(er * p.AU + eh * enb);
-                    const uint32_t dst = sbase + 16u * (uint32_t)p.RS + (uint32_t)(er * p.AS + eh * enb * 4);
-                    for (int q4 = 0; q4 < enb; q4 += 8) {
-                        const uint2 b8 = lds64(src + q4);
-                        float f[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const uint32_t byte = ((i < 4 ? b8.x : b8.y) >> (8 * (i & 3))) & 0xffu;
-                            f[i] = fmaf(lds32f(c256_u32 + 4u * byte), sc, dq_off);
-                        }
-                        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst + q4 * 4), "f"(f[0]), "f"(f[1]), "f"(f[2]), "f"(f[3]) : "memory");
-                        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst + q4 * 4 + 16), "f"(f[4]), "f"(f[5]), "f"(f[6]), "f"(f[7]) : "memory");
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(ready0 + slot_e * 8);
-                advance(ce);
-                ++expanded;
-            };
-            while (ci.tile0 < ntiles) {
-                const int slot_i = issued % p.NS;
-                if (issued >= p.NS) mbar_wait(empty0 + slot_i * 8, (uint32_t)(((issued / p.NS) & 1) ^ 1), abort_flag, 2, issued);
-                if (lane == 0) {
-                    const int row0 = r0 + (ci.tile0 + ci.j) * 16;
-                    const uint32_t fullb = full0 + slot_i * 8;
-                    const uint32_t sbase = ring_u32 + (uint32_t)slot_i * (uint32_t)p.stage_bytes;
-                    mbar_expect_tx(fullb, (uint32_t)(ci.half ? 8 : 16) * (uint32_t)(p.RS + p.AU));
-                    tma_load_2d(sbase, ci.half ? &p.wmap8 : &p.wmap16, ci.seg * p.SB * 4, row0, fullb);
-                    tma_load_2d(sbase + 16 * (p.RS + p.AS), ci.half ? &p.amap8 : &p.amap16, ci.seg * p.SB, row0, fullb);
-                }
-                __syncwarp();
-                advance(ci);
-                ++issued;
-                if (issued - expanded > lag) expand();
-            }
-            while (expanded < issued) expand();
-        } else {
         int stage = 0, slot = 0;
         uint32_t parity = 0;
         for (int tile0 = 0; tile0 < ntiles;) {
@@ -411,7 +347,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                 }
             }
             tile0 += nt_here;
-        }
         }
         if (p.pf_packed) {
             // every load of this launch is in flight: pull the head of this CTA's share of the next
@@ -445,6 +380,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
                      x_row_bytes, xbar);
     }
     lut_build<T, CW>(lut_ptr, level, warp, lane);
+    float dq_off = 0.0f;
+    if (DQ) {
+        if (tid < 256) reinterpret_cast<float*>(smem + p.off_c256)[tid] = __ldg(p.code256 + tid);
+        dq_off = __ldg(p.offset);
+    }
+    const uint32_t c256 = s0 + (uint32_t)p.off_c256;
     // barriers armed (producer) and table complete (compute warps) for every compute warp after this
     asm volatile("bar.sync 2, %0;" ::"n"((CW + 1) * 32) : "memory");
     griddep_launch();
@@ -541,7 +482,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     uint32_t a_off[BPW];
 #pragma unroll
     for (int bi = 0; bi < BPW; ++bi) a_off[bi] = (uint32_t)(g * p.RS + (b0 + bi) * 32 + q * 8);
-    const uint32_t am_off = (uint32_t)(16 * p.RS + g * p.AS + b0 * 4);
+    const uint32_t am_off = (uint32_t)(16 * p.RS + g * p.AS + b0 * (DQ ? 1 : 4));
     const uint32_t rs8 = 8u * (uint32_t)p.RS, as8 = 8u * (uint32_t)p.AS;
     const uint32_t stage_bytes = (uint32_t)p.stage_bytes;
     const int NS = p.NS;
@@ -581,12 +522,24 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_staged_kernel(const __g
     };
 
     // one stage: wait for the box, compute, hand the slot back
-    // (DQ: the producer warp signals `ready` once the stage's absmax rows hold fp32 values)
+    // DQ: second-level scales of this lane's rows (g, g+8 of the tile starting at row0_) in segment seg_: one
+    // scale per 256 consecutive first-level blocks of the flattened weight; SB (16 or 32) divides K/64, so the
+    // SB blocks of a row's segment start at a multiple of SB and never straddle a multiple of 256
+    auto load_scales = [&](float (&sc)[2], int row0_, int seg_) {
+        if (DQ) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int row = min(split_gu ? row0_ + g + hh * n_own : row0_ + g + 8 * hh, p.N - 1);
+                sc[hh] = __ldg(p.scale2 + (((int64_t)row * p.KB + seg_ * p.SB) >> 8));
+            }
+        }
+    };
 #define NF4_DO_STAGE(HALF_, XF_, ACC_, ROW0_, SEG_)                                                                 \
     do {                                                                                                           \
+        float sc_[2];                                                                                              \
+        load_scales(sc_, ROW0_, SEG_);                                                                             \
         mbar_wait(full0 + slot * 8, parity, abort_flag, 1, stage);                                                  \
-        if (DQ) mbar_wait(ready0 + slot * 8, parity, abort_flag, 1, stage);                                         \
-        stage_compute<T, NT, BPW, HALF_>(ring_u32 + slot * stage_bytes, a_off, am_off, rs8, as8, window_lane, XF_, ACC_); \
+        stage_compute<T, NT, BPW, HALF_, DQ>(ring_u32 + slot * stage_bytes, a_off, am_off, rs8, as8, window_lane, XF_, ACC_, sc_, c256, dq_off); \
         __syncwarp();                                                                                              \
         if (lane == 0) mbar_arrive(empty0 + slot * 8);                                                              \
         ++stage;                                                                                                   \
@@ -916,9 +869,8 @@ int gemv_staged_try(const void* x, int M, int K, const uint8_t* packed, const fl
         }
     }
     p.RS = SB * 32 + 32;
-    p.AS = SB * 4 + 16;
-    p.AU = dq ? SB + 16 : 0;       // the uint8 box of a double-quantized stage sits behind the fp32 rows it is expanded into
-    p.stage_bytes = 16 * p.RS + 16 * p.AS + 16 * p.AU;
+    p.AS = dq ? SB + 16 : SB * 4 + 16;
+    p.stage_bytes = 16 * p.RS + 16 * p.AS;
     p.prologue = opt.prologue; p.norm_w = opt.norm_w; p.eps = opt.eps; p.epilogue = opt.epilogue;
     if (opt.epilogue == 1 && (N % 2 != 0)) return -2;
     p.x_stride = (opt.prologue == 2 ? 4 : 2) * K + 16;
