@@ -81,9 +81,9 @@ class NF4Decoder:
         self.tp_rank, self.tp_size, self.group = tp_rank, tp_size, group
         self.lib = _lib.load()
         if attn_splits is None:
-            # enough CTAs (kv heads x rows x splits) to cover the SMs twice, but at least ~128 cached
-            # positions per CTA (shorter ranges are all start-up and merge)
-            attn_splits = max(1, min(16, 296 // max(1, (cfg.n_kv_heads // tp_size) * batch), max_seq // 128))
+            # enough CTAs (kv heads x rows x splits) to cover the SMs twice, but at least ~96 cached
+            # positions per CTA (shorter ranges are all start-up and merge); the rule of functional.attn_splits
+            attn_splits = max(1, min(16, 296 // max(1, (cfg.n_kv_heads // tp_size) * batch), max_seq // 96))
         self.attn_splits = attn_splits
         # fused: RMSNorm and SiLU*up run as prologues of the following GEMV (where the activations fit
         # in shared memory), rotary embedding + KV append + attention + merge are one launch.
