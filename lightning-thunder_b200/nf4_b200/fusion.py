@@ -136,7 +136,9 @@ def _attn_prefill(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache,
     return y.view(x.shape).add_(x)
 
 
-def _attn_block_impl(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv):
+def _attn_block_impl(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv,
+                     nxt_w=None, nxt_a=None, nxt_N=0, nxt_K=0):
+    # (nxt_*: the weight the launch after this block streams, hinted to this block's last GEMV)
     F = functional
     D = x.shape[-1]
     if x.dim() == 3 and x.shape[1] > 1:
@@ -147,11 +149,11 @@ def _attn_block_impl(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cac
     qkv = _gemv(x2, _span((wq, wk, wv), "q/k/v weight"), _span((aq, ak, av), "q/k/v absmax"), code,
                 (Hq + 2 * Hkv) * HEAD_DIM, D, norm_w=norm_w, eps=eps, next_weight=(wo, ao, D, Hq * HEAD_DIM))
     att = F.attn_decode_fused(qkv, positions, k_cache, v_cache, Hq, Hkv, theta, pdl=True)
-    y = _gemv(att, wo, ao, code, D, Hq * HEAD_DIM, residual=x2)
+    y = _gemv(att, wo, ao, code, D, Hq * HEAD_DIM, residual=x2, next_weight=(nxt_w, nxt_a, nxt_N, nxt_K) if nxt_w is not None else None)
     return y.view(x.shape)
 
 
-def _mlp_block_impl(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim):
+def _mlp_block_impl(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim, nxt_w=None, nxt_a=None, nxt_N=0, nxt_K=0):
     F = functional
     D = h.shape[-1]
     B = h.numel() // D
@@ -168,7 +170,7 @@ def _mlp_block_impl(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim):
     else:
         gu = _gemv(h2, packed, absmax, code, 2 * Fdim, D, norm_w=norm_w, eps=eps)
         act = F.silu_mul(gu, Fdim, interleaved=False)
-    y = _gemv(act, w2, a2, code, D, Fdim, residual=h2)
+    y = _gemv(act, w2, a2, code, D, Fdim, residual=h2, next_weight=(nxt_w, nxt_a, nxt_N, nxt_K) if nxt_w is not None else None)
     return y.view(h.shape)
 
 
@@ -192,10 +194,11 @@ def get_fusion_symbols():
     def positions_meta(input_pos, B, T):
         return TensorProxy(like=input_pos, shape=(B,) if T == 1 else (T,), dtype=thunder.dtypes.int32)
 
-    def attn_block_meta(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv):
+    def attn_block_meta(x, norm_w, eps, wq, aq, wk, ak, wv, av, wo, ao, code, k_cache, v_cache, positions, theta, Hq, Hkv,
+                        nxt_w=None, nxt_a=None, nxt_N=0, nxt_K=0):
         return TensorProxy(like=x)
 
-    def mlp_block_meta(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim):
+    def mlp_block_meta(h, norm_w, eps, w1, a1, w3, a3, w2, a2, code, Fdim, nxt_w=None, nxt_a=None, nxt_N=0, nxt_K=0):
         return TensorProxy(like=h)
 
     def norm_linear_meta(x, norm_w, eps, w, a, code, N):
@@ -652,6 +655,21 @@ class NF4DecodeFusion(Transform):
                     if all(n is not None for n in names) and len(set(names)) == len(names):
                         self._rehome(names)
 
+        # the weight each block's last GEMV should hint: the first one the next block (in trace order) streams
+        # (only the first tensor of a q|k|v or gate|up group, with its own row count: the hint makes the kernel touch
+        # that memory, and whether the group is still adjacent in memory is only known at call time)
+        def first_weight(f):
+            if f.kind == "attn":
+                a = f.args
+                return a["wq"], a["aq"], a["Hq"] * HEAD_DIM, int(a["x"].shape[-1])
+            if f.kind == "mlp":
+                return f.args[3], f.args[4], f.args[10], int(f.args[0].shape[-1])
+            return f.args[3], f.args[4], f.args[6], int(f.args[0].shape[-1])
+
+        ordered = sorted(found, key=lambda f: f.anchor)
+        hint = {}
+        for cur, nxt in zip(ordered, ordered[1:]):
+            hint[cur.anchor] = first_weight(nxt)
         by_anchor = {f.anchor: f for f in found}
         new_trace = from_trace(computation_trace)
         new_bsyms = []
@@ -673,9 +691,10 @@ class NF4DecodeFusion(Transform):
                         pos32[key] = p32
                     new_bsyms.append(sym["attn_block"].bind(
                         a["x"], a["nw"], a["eps"], a["wq"], a["aq"], a["wk"], a["ak"], a["wv"], a["av"], a["wo"], a["ao"],
-                        a["code"], a["k_cache"], a["v_cache"], p32, float(theta), a["Hq"], a["Hkv"], output=f.out))
+                        a["code"], a["k_cache"], a["v_cache"], p32, float(theta), a["Hq"], a["Hkv"],
+                        *hint.get(f.anchor, (None, None, 0, 0)), output=f.out))
                 elif f.kind == "mlp":
-                    new_bsyms.append(sym["mlp_block"].bind(*f.args, output=f.out))
+                    new_bsyms.append(sym["mlp_block"].bind(*f.args, *hint.get(f.anchor, (None, None, 0, 0)), output=f.out))
                 else:
                     new_bsyms.append(sym["norm_linear"].bind(*f.args, output=f.out))
                 self.fused[f.kind] += 1
